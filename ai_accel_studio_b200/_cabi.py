@@ -1,0 +1,106 @@
+"""ctypes binding of the C ABI declared in ``include/qgemv_b200.h``.
+
+Nothing here touches torch: callers pass raw device addresses, sizes and a stream handle.
+A missing or unloadable library is a hard error -- there is no fallback implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libqgemv_b200.so"
+
+OK = 0
+ACT = {"none": 0, "relu": 1, "silu": 2, "swish": 2}
+F16, BF16, F32 = 0, 1, 2
+KERNEL = {"auto": 0, "simt": 1, "mma": 2}
+MAX_M = 4
+ABI_VERSION = 1
+
+EXPORTS = ("qgemv_run", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
+           "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem")
+
+
+class Problem(C.Structure):
+    """``struct qgemv_problem`` (field order and types must match the header)."""
+    _fields_ = [
+        ("bits", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k_padded", C.c_int32),
+        ("k_original", C.c_int32), ("group", C.c_int32), ("act", C.c_int32), ("x_dtype", C.c_int32),
+        ("outliers", C.c_int32), ("rank", C.c_int32), ("kernel", C.c_int32), ("reserved", C.c_int32),
+        ("x", C.c_void_p), ("ldx", C.c_int64),
+        ("packed", C.c_void_p), ("ldp", C.c_int64),
+        ("scales", C.c_void_p), ("lds", C.c_int64),
+        ("bias", C.c_void_p),
+        ("outlier_idx", C.c_void_p),
+        ("outlier_w", C.c_void_p), ("ldow", C.c_int64),
+        ("res_u", C.c_void_p), ("ldu", C.c_int64),
+        ("res_v", C.c_void_p), ("ldv", C.c_int64),
+        ("y", C.c_void_p), ("ldy", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class QgemvError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"qgemv error {code}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib():
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m ai_accel_studio_b200.build` "
+            "(needs nvcc with sm_100a support). There is no fallback implementation.")
+    l = C.CDLL(str(LIB_PATH))
+    l.qgemv_run.argtypes = [C.POINTER(Problem), C.c_void_p]
+    l.qgemv_run.restype = C.c_int
+    l.qgemv_workspace_bytes.argtypes = [C.c_int] * 6
+    l.qgemv_workspace_bytes.restype = C.c_size_t
+    l.qgemv_plan_name.argtypes = [C.POINTER(Problem)]
+    l.qgemv_plan_name.restype = C.c_char_p
+    l.qdequant.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
+                           C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    l.qdequant.restype = C.c_int
+    l.qunpack_codes.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_void_p]
+    l.qunpack_codes.restype = C.c_int
+    l.qgemv_error_string.argtypes = []
+    l.qgemv_error_string.restype = C.c_char_p
+    l.qgemv_abi_version.argtypes = []
+    l.qgemv_abi_version.restype = C.c_int
+    l.qgemv_sizeof_problem.argtypes = []
+    l.qgemv_sizeof_problem.restype = C.c_size_t
+    if l.qgemv_sizeof_problem() != C.sizeof(Problem):
+        raise RuntimeError("struct qgemv_problem layout mismatch between the binding and the library; rebuild it")
+    if l.qgemv_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"{LIB_PATH} has ABI version {l.qgemv_abi_version()}, expected {ABI_VERSION}; rebuild it")
+    _lib = l
+    return l
+
+
+def last_error() -> str:
+    return lib().qgemv_error_string().decode()
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise QgemvError(code, last_error())
+
+
+def workspace_bytes(bits: int, m: int, n: int, k_padded: int, group: int, rank: int) -> int:
+    return int(lib().qgemv_workspace_bytes(bits, m, n, k_padded, group, rank))
+
+
+def run(problem: Problem, stream: int) -> None:
+    check(lib().qgemv_run(C.byref(problem), C.c_void_p(stream)))
+
+
+def plan_name(problem: Problem):
+    r = lib().qgemv_plan_name(C.byref(problem))
+    return None if r is None else r.decode()

@@ -1,0 +1,138 @@
+// C ABI entry points: argument validation, kernel selection, launch.  See include/qgemv_b200.h.
+#include <cstdarg>
+#include <cstdio>
+
+#include "qgemv_common.cuh"
+
+namespace qgemv {
+
+static thread_local char g_error[512] = "no error";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        // Clear the (non-sticky) launch error so that the next call starts clean.
+        (void)cudaGetLastError();
+        set_error("%s: %s", what, cudaGetErrorString(e));
+        return QGEMV_ERR_LAUNCH;
+    }
+    return QGEMV_OK;
+}
+
+namespace {
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Largest load unit (bytes) the CUDA-core kernel may use for this problem.
+int simt_unit_bytes(const qgemv_problem& p) {
+    const int cpb = 8 / p.bits;
+    if (aligned(p.packed, 16) && p.ldp % 16 == 0 && p.group % (16 * cpb) == 0) return 16;
+    if (aligned(p.packed, 4) && p.ldp % 4 == 0 && p.group % (4 * cpb) == 0) return 4;
+    return 1;
+}
+
+int validate(const qgemv_problem* p) {
+    if (!p) { set_error("qgemv_run: problem is NULL"); return QGEMV_ERR_BAD_ARG; }
+    if (p->bits != 2 && p->bits != 4) { set_error("qgemv_run: bits must be 2 or 4 (got %d)", p->bits); return QGEMV_ERR_BAD_ARG; }
+    if (p->m < 1 || p->m > QGEMV_MAX_M) { set_error("qgemv_run: M must be 1..%d (got %d); larger batches use the dequantise + GEMM path", QGEMV_MAX_M, p->m); return QGEMV_ERR_BAD_ARG; }
+    if (p->n < 1 || p->k_padded < 1 || p->k_original < 1 || p->k_original > p->k_padded) { set_error("qgemv_run: bad N / K (n=%d, k_padded=%d, k_original=%d)", p->n, p->k_padded, p->k_original); return QGEMV_ERR_BAD_ARG; }
+    if (!p->x || !p->packed || !p->scales || !p->y) { set_error("qgemv_run: x, packed, scales and y must be non-null"); return QGEMV_ERR_BAD_ARG; }
+    if (p->act < QGEMV_ACT_NONE || p->act > QGEMV_ACT_SILU) { set_error("qgemv_run: unknown activation %d", p->act); return QGEMV_ERR_BAD_ARG; }
+    if (p->x_dtype != QGEMV_F16 && p->x_dtype != QGEMV_BF16) { set_error("qgemv_run: activations must be fp16 or bf16"); return QGEMV_ERR_BAD_ARG; }
+    if (p->kernel < QGEMV_KERNEL_AUTO || p->kernel > QGEMV_KERNEL_MMA) { set_error("qgemv_run: unknown kernel selector %d", p->kernel); return QGEMV_ERR_BAD_ARG; }
+    if (p->outliers < 0 || (p->outliers > 0 && (!p->outlier_idx || !p->outlier_w))) { set_error("qgemv_run: outliers=%d needs outlier_idx and outlier_w", p->outliers); return QGEMV_ERR_BAD_ARG; }
+    if (p->rank < 0 || (p->rank > 0 && (!p->res_u || !p->res_v))) { set_error("qgemv_run: rank=%d needs res_u and res_v", p->rank); return QGEMV_ERR_BAD_ARG; }
+    if (p->rank > kMaxRank) { set_error("qgemv_run: residual rank %d exceeds the limit of %d", p->rank, kMaxRank); return QGEMV_ERR_TOO_LARGE; }
+    const int cpb = 8 / p->bits;
+    if (p->group < cpb || p->group % cpb || p->k_padded % p->group) { set_error("qgemv_run: group=%d must be a multiple of %d and divide k_padded=%d", p->group, cpb, p->k_padded); return QGEMV_ERR_SHAPE; }
+    if (p->ldx < p->k_padded || p->ldy < p->n || p->ldp < (int64_t)p->k_padded / cpb || p->lds < p->k_padded / p->group) { set_error("qgemv_run: a leading dimension is smaller than its row"); return QGEMV_ERR_SHAPE; }
+    if (p->outliers > 0 && p->ldow < p->outliers) { set_error("qgemv_run: ldow < outliers"); return QGEMV_ERR_SHAPE; }
+    if (p->rank > 0 && (p->ldu < p->rank || p->ldv < p->k_original)) { set_error("qgemv_run: ldu < rank or ldv < k_original"); return QGEMV_ERR_SHAPE; }
+    if (!aligned(p->x, 2) || !aligned(p->y, 2) || !aligned(p->scales, 2)) { set_error("qgemv_run: 16-bit tensors must be 2-byte aligned"); return QGEMV_ERR_ALIGN; }
+    const size_t need = qgemv_workspace_bytes(p->bits, p->m, p->n, p->k_padded, p->group, p->rank);
+    if (!p->workspace || p->workspace_bytes < need) { set_error("qgemv_run: workspace of %zu bytes required (got %zu)", need, p->workspace ? p->workspace_bytes : (size_t)0); return QGEMV_ERR_WORKSPACE; }
+    if (!aligned(p->workspace, 256)) { set_error("qgemv_run: workspace must be 256-byte aligned"); return QGEMV_ERR_ALIGN; }
+    return QGEMV_OK;
+}
+
+Args make_args(const qgemv_problem& p) {
+    Args a{};
+    a.x = p.x; a.ldx = p.ldx;
+    a.packed = p.packed; a.ldp = p.ldp;
+    a.scales = static_cast<const __half*>(p.scales); a.lds = p.lds;
+    a.bias = static_cast<const __half*>(p.bias);
+    a.oidx = p.outlier_idx;
+    a.ow = static_cast<const __half*>(p.outlier_w); a.ldow = p.ldow;
+    a.ru = static_cast<const __half*>(p.res_u); a.ldu = p.ldu;
+    a.rv = static_cast<const __half*>(p.res_v); a.ldv = p.ldv;
+    a.y = p.y; a.ldy = p.ldy;
+    char* ws = static_cast<char*>(p.workspace);
+    a.t = reinterpret_cast<float*>(ws + kWsTOff);
+    a.counters = reinterpret_cast<int*>(ws + kWsCounterOff);
+    a.partial = reinterpret_cast<float*>(ws + kWsPartialOff);
+    a.m = p.m; a.n = p.n; a.kpad = p.k_padded; a.korig = p.k_original; a.group = p.group;
+    a.act = p.act; a.oc = p.outliers; a.rank = p.rank;
+    a.splits = 1; a.kspan = p.k_padded;
+    return a;
+}
+
+}  // namespace
+}  // namespace qgemv
+
+using namespace qgemv;
+
+extern "C" int qgemv_abi_version(void) { return QGEMV_ABI_VERSION; }
+
+extern "C" const char* qgemv_error_string(void) { return g_error; }
+
+extern "C" size_t qgemv_sizeof_problem(void) { return sizeof(qgemv_problem); }
+
+extern "C" size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, int group, int rank) {
+    (void)bits; (void)m; (void)n; (void)k_padded; (void)group; (void)rank;
+    // Shape independent: residual projections + counters + kMaxPartialFloats split-K partials.
+    // The planner never picks a split count whose partial sums would not fit.
+    return kWsPartialOff + kMaxPartialFloats * sizeof(float);
+}
+
+extern "C" const char* qgemv_plan_name(const qgemv_problem* p) {
+    if (validate(p) != QGEMV_OK) return nullptr;
+    if (p->kernel != QGEMV_KERNEL_SIMT) {
+        const MmaPlan plan = plan_mma(*p);
+        if (plan.ok) return plan.name;
+        if (p->kernel == QGEMV_KERNEL_MMA) return nullptr;
+    }
+    return simt_name(p->bits, p->m, simt_unit_bytes(*p));
+}
+
+extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
+    const int v = validate(p);
+    if (v != QGEMV_OK) return v;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Args a = make_args(*p);
+    const bool bf16 = p->x_dtype == QGEMV_BF16;
+
+    MmaPlan plan{};
+    bool use_mma = false;
+    if (p->kernel != QGEMV_KERNEL_SIMT) {
+        plan = plan_mma(*p);
+        use_mma = plan.ok;
+        if (!use_mma && p->kernel == QGEMV_KERNEL_MMA) {
+            set_error("qgemv_run: the tensor-core-assisted kernel does not support this shape "
+                      "(needs 16-byte aligned rows and group in {32,64,128,256} for INT4 / {64,128,256} for INT2)");
+            return QGEMV_ERR_SHAPE;
+        }
+    }
+    if (a.rank > 0) {
+        const int r = launch_residual_t(a, bf16, s);
+        if (r != QGEMV_OK) return r;
+    }
+    if (use_mma) return launch_mma(a, p->bits, bf16, plan, s);
+    return launch_simt(a, p->bits, bf16, simt_unit_bytes(*p), s);
+}

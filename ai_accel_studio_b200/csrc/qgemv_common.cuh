@@ -1,0 +1,75 @@
+// Shared declarations for the packed groupwise INT2 / INT4 GEMV library (sm_100a).
+#pragma once
+
+#include <cstdint>
+#include <cstddef>
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include "../../include/qgemv_b200.h"
+
+namespace qgemv {
+
+// Workspace layout (bytes from the 256-byte aligned base the caller passes):
+//   [0, 1024)            residual projections t[m][r] = sum_k V[r,k] x[m,k], fp32, QGEMV_MAX_M x 64
+//   [1024, 1024+4*4096)  split-K arrival counters, one int32 per row block (zero between calls)
+//   [WS_PARTIAL_OFF, ..) split-K partial sums, fp32 [splits][M][N]
+constexpr int    kMaxRank        = 64;
+constexpr size_t kWsTOff         = 0;
+constexpr size_t kWsCounterOff   = 1024;
+constexpr int    kWsMaxCounters  = 4096;
+constexpr size_t kWsPartialOff   = kWsCounterOff + sizeof(int) * kWsMaxCounters;   // 17408, 256-aligned
+constexpr size_t kMaxPartialFloats = size_t(1) << 20;                             // 4 MiB of fp32 partial sums
+
+// Device-side view of one problem; a trivially copyable kernel parameter.
+struct Args {
+    const void* x;            long long ldx;
+    const uint8_t* packed;    long long ldp;
+    const __half* scales;     long long lds;
+    const __half* bias;
+    const int32_t* oidx;
+    const __half* ow;         long long ldow;
+    const __half* ru;         long long ldu;
+    const __half* rv;         long long ldv;
+    void* y;                  long long ldy;
+    float* t;                 // residual projections (workspace)
+    int* counters;            // split-K counters (workspace)
+    float* partial;           // split-K partials (workspace)
+    int m, n, kpad, korig, group, act, oc, rank;
+    int splits;               // number of K splits (grid.y)
+    int kspan;                // codes per K split (multiple of the group)
+};
+
+template <bool BF16> struct Act16;
+template <> struct Act16<false> {
+    using T = __half;
+    static __device__ __forceinline__ float to_float(T v) { return __half2float(v); }
+    static __device__ __forceinline__ T from_float(float v) { return __float2half_rn(v); }
+};
+template <> struct Act16<true> {
+    using T = __nv_bfloat16;
+    static __device__ __forceinline__ float to_float(T v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ T from_float(float v) { return __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == QGEMV_ACT_RELU) return fmaxf(v, 0.0f);
+    if (act == QGEMV_ACT_SILU) return v / (1.0f + __expf(-v));
+    return v;
+}
+
+// Host-side error reporting (thread local).
+void set_error(const char* fmt, ...);
+int  check_launch(const char* what);
+
+// Launchers implemented in the kernel translation units.
+int launch_residual_t(const Args& a, bool bf16, cudaStream_t s);
+int launch_simt(const Args& a, int bits, bool bf16, int unit_bytes, cudaStream_t s);
+const char* simt_name(int bits, int m, int unit_bytes);
+
+struct MmaPlan { bool ok; int splits; int kspan; int rows_per_cta; const char* name; };
+MmaPlan plan_mma(const qgemv_problem& p);
+int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& plan, cudaStream_t s);
+
+}  // namespace qgemv

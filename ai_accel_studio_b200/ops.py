@@ -1,0 +1,171 @@
+"""torch custom ops over the C ABI (namespace ``b200q``).
+
+The ops are registered with ``torch.library`` together with fake (meta) implementations, so
+``torch.compile`` traces through them without graph breaks and CUDA-graph capture records the
+launches.  Each call passes raw device pointers and ``torch.cuda.current_stream()`` to the
+shared library; nothing is synchronised and the only allocation is the output tensor.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _cabi
+
+_DT = {torch.float16: _cabi.F16, torch.bfloat16: _cabi.BF16, torch.float32: _cabi.F32}
+_DT_NAME = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
+
+# One scratch buffer per device, shared by all calls issued on that device.  Calls are
+# stream-ordered in the decode path, and the kernels restore the buffer's invariant (all
+# split-K counters zero) before they finish, so it never needs clearing between calls.
+_WORKSPACE: dict[int, torch.Tensor] = {}
+
+
+def _device_index(dev: torch.device) -> int:
+    return dev.index if dev.index is not None else torch.cuda.current_device()
+
+
+def ensure_workspace(device) -> torch.Tensor:
+    """Allocate (once, zero-filled) the per-device scratch buffer.  Must first run outside
+    CUDA-graph capture; module construction / ``.to(device)`` and the first eager call do."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("qgemv workspace lives in CUDA memory")
+    idx = _device_index(device)
+    ws = _WORKSPACE.get(idx)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the qgemv scratch buffer must be created before CUDA-graph capture starts: "
+                               "call ai_accel_studio_b200.ops.ensure_workspace(device) first")
+        nbytes = _cabi.workspace_bytes(4, _cabi.MAX_M, 1, 256, 128, 64)   # shape independent
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=torch.device("cuda", idx))
+        _WORKSPACE[idx] = ws
+    return ws
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this build has no CPU path")
+
+
+def _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws,
+             bits, group, k_original, act, kernel) -> _cabi.Problem:
+    m, kpad = x.shape
+    p = _cabi.Problem()
+    p.bits, p.m, p.n, p.k_padded, p.k_original, p.group = bits, m, packed.shape[0], kpad, k_original, group
+    p.act, p.x_dtype, p.kernel = act, _DT[x.dtype], kernel
+    p.x, p.ldx = x.data_ptr(), x.stride(0)
+    p.packed, p.ldp = packed.data_ptr(), packed.stride(0)
+    p.scales, p.lds = scales.data_ptr(), scales.stride(0)
+    p.bias = bias.data_ptr() if bias is not None else None
+    oc = 0 if outlier_idx is None else int(outlier_idx.numel())
+    p.outliers = oc
+    if oc:
+        p.outlier_idx, p.outlier_w, p.ldow = outlier_idx.data_ptr(), outlier_weight.data_ptr(), outlier_weight.stride(0)
+    rank = 0 if res_u is None else int(res_u.shape[1])
+    p.rank = rank
+    if rank:
+        p.res_u, p.ldu, p.res_v, p.ldv = res_u.data_ptr(), res_u.stride(0), res_v.data_ptr(), res_v.stride(0)
+    p.y, p.ldy = y.data_ptr(), y.stride(0)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    return p
+
+
+def _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits):
+    _require_cuda(x, "x")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("the packed decode path requires fp16/bf16 activations")
+    if x.ndim != 2 or x.shape[0] > _cabi.MAX_M or x.shape[0] < 1:
+        raise ValueError("decode-specialized path is for [M,K] with 1 <= M <= 4")
+    if x.stride(1) != 1:
+        raise ValueError("x must have unit stride along K")
+    if packed.dtype != torch.uint8 or scales.dtype != torch.float16:
+        raise RuntimeError("packed must be uint8 and scales float16")
+    if packed.shape[1] * (8 // bits) != x.shape[1]:
+        raise ValueError("input must already be padded to packed K")
+    for name, t, dt in (("bias", bias, torch.float16), ("outlier_weight", outlier_weight, torch.float16),
+                        ("res_u", res_u, torch.float16), ("res_v", res_v, torch.float16),
+                        ("outlier_idx", outlier_idx, torch.int32)):
+        if t is not None:
+            _require_cuda(t, name)
+            if t.dtype != dt:
+                raise RuntimeError(f"{name} must be {dt}")
+            if t.ndim >= 1 and t.numel() and t.stride(-1) != 1:
+                raise ValueError(f"{name} must have unit inner stride")
+
+
+@torch.library.custom_op("b200q::gemv", mutates_args=())
+def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+         outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
+         res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
+         bits: int, group: int, k_original: int, act: int, kernel: int) -> torch.Tensor:
+    """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4."""
+    _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits)
+    if outlier_idx is not None and outlier_idx.numel() == 0:
+        outlier_idx = outlier_weight = None
+    if res_u is not None and res_u.numel() == 0:
+        res_u = res_v = None
+    ws = ensure_workspace(x.device)
+    y = torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device=x.device)
+    prob = _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws,
+                    bits, group, k_original, act, kernel)
+    with torch.cuda.device(x.device):
+        _cabi.run(prob, torch.cuda.current_stream().cuda_stream)
+    return y
+
+
+@gemv.register_fake
+def _(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits, group, k_original, act, kernel):
+    return x.new_empty((x.shape[0], packed.shape[0]))
+
+
+@torch.library.custom_op("b200q::dequant", mutates_args=())
+def dequant(packed: torch.Tensor, scales: torch.Tensor, bits: int, group: int, k_original: int,
+            dtype_name: str) -> torch.Tensor:
+    """Dense [N, k_original] matrix, bit-identical to the torch expression of the reference."""
+    _require_cuda(packed, "packed")
+    _require_cuda(scales, "scales")
+    dtype = _DT_NAME[dtype_name]
+    if packed.dtype != torch.uint8 or scales.dtype != torch.float16 or packed.stride(1) != 1 or scales.stride(1) != 1:
+        raise RuntimeError("packed must be uint8, scales float16, both with unit inner stride")
+    n, kpad = packed.shape[0], packed.shape[1] * (8 // bits)
+    out = torch.empty((n, k_original), dtype=dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _cabi.check(_cabi.lib().qdequant(bits, packed.data_ptr(), packed.stride(0), scales.data_ptr(), scales.stride(0),
+                                         n, kpad, k_original, group, out.data_ptr(), out.stride(0), _DT[dtype],
+                                         torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+@dequant.register_fake
+def _(packed, scales, bits, group, k_original, dtype_name):
+    return packed.new_empty((packed.shape[0], k_original), dtype=_DT_NAME[dtype_name])
+
+
+@torch.library.custom_op("b200q::unpack_codes", mutates_args=())
+def unpack_codes(packed: torch.Tensor, bits: int) -> torch.Tensor:
+    """One uint8 code per weight, [N, Kpad]."""
+    _require_cuda(packed, "packed")
+    if packed.dtype != torch.uint8 or packed.stride(1) != 1:
+        raise RuntimeError("packed must be uint8 with unit inner stride")
+    n, kpad = packed.shape[0], packed.shape[1] * (8 // bits)
+    out = torch.empty((n, kpad), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _cabi.check(_cabi.lib().qunpack_codes(bits, packed.data_ptr(), packed.stride(0), n, kpad,
+                                              out.data_ptr(), out.stride(0), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+@unpack_codes.register_fake
+def _(packed, bits):
+    return packed.new_empty((packed.shape[0], packed.shape[1] * (8 // bits)))
+
+
+def plan_name(x, packed, scales, bits, group, k_original, outliers=0, rank=0, kernel="auto"):
+    """Name of the kernel variant a call of this shape would launch (no launch happens)."""
+    ws = ensure_workspace(x.device)
+    y = torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device=x.device)
+    p = _problem(x, packed, scales, None, None, None, None, None, y, ws, bits, group, k_original, 0,
+                 _cabi.KERNEL[kernel])
+    return _cabi.plan_name(p)

@@ -1,0 +1,109 @@
+"""The drop-in Linear wrappers on the GPU: fixtures made by the reference modules, the M > 4
+path, state-dict round trips, CUDA-graph capture and torch.compile."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from oracle import qgemv_oracle as O
+from conftest import assert_within_tolerance
+from ai_accel_studio_b200.optimize import HybridInt2Linear, HybridInt4Linear
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(c, z):
+    nm = c["name"]
+    lin = nn.Linear(c["k"], c["n"], bias=c["bias"])
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(z[nm + ".w"]))
+        if c["bias"]:
+            lin.bias.copy_(torch.from_numpy(z[nm + ".srcbias"]))
+    arms = torch.from_numpy(z[nm + ".arms"]) if c["aware"] else None
+    if c["bits"] == 2:
+        return HybridInt2Linear(lin, c["group"], arms, c["requested"], c["rank"])
+    return HybridInt4Linear(lin, c["group"], arms, c["requested"])
+
+
+def test_modules_reproduce_reference_outputs(small_cases):
+    z, meta = small_cases
+    for c in meta["hybrid_cases"]:
+        nm = c["name"]
+        mod = _build(c, z).to("cuda")
+        host = O.PackedWeight(c["bits"], z[nm + ".packed"], z[nm + ".scales"], c["k"], c["padded_k"], c["group"])
+        kw = dict(bias=z[nm + ".bias"] if c["bias"] else None, outlier_idx=z[nm + ".outlier_idx"],
+                  outlier_weight=z[nm + ".outlier_weight"],
+                  res_u=z[nm + ".res_u"] if c["rank"] else None, res_v=z[nm + ".res_v"] if c["rank"] else None)
+        for m in (1, 2, 3, 4, 6):       # 6 rows takes the dequantise + GEMM path
+            x = torch.from_numpy(z[f"{nm}.x{m}"])
+            y = mod(x.cuda())
+            assert y.dtype == torch.float16 and tuple(y.shape) == (m, c["n"])
+            ref = O.gemv_f32(x.numpy(), host, **kw)
+            if m <= 4:
+                assert_within_tolerance(y.float().cpu().numpy(), ref, f"{nm} m={m}")
+            # against what the reference module returned on the CPU (fp16 arithmetic on both sides)
+            assert np.abs(y.float().cpu().numpy() - z[f"{nm}.y{m}"].astype(np.float32)).max() < 8e-3, (nm, m)
+        x3 = torch.from_numpy(z[nm + ".x3d"])
+        y3 = mod(x3.cuda())
+        assert tuple(y3.shape) == (2, 2, c["n"])
+        assert np.abs(y3.float().cpu().numpy() - z[nm + ".y3d"].astype(np.float32)).max() < 8e-3
+
+
+def test_state_dict_round_trip_on_device(small_cases):
+    z, meta = small_cases
+    c = meta["hybrid_cases"][1]
+    src = _build(c, z)
+    dst = HybridInt2Linear(nn.Linear(c["k"], c["n"], bias=True), c["group"], None, c["requested"], c["rank"]).to("cuda")
+    dst.load_state_dict(src.state_dict(), strict=False)
+    x = torch.from_numpy(z[c["name"] + ".x2"]).cuda()
+    assert torch.equal(dst(x), src.to("cuda")(x))
+
+
+def test_int4_residual_extension():
+    torch.manual_seed(0)
+    lin = nn.Linear(512, 96, bias=False)
+    plain = HybridInt4Linear(lin, 128, None, 8).cuda()
+    u, v = torch.randn(96, 8) * 0.05, torch.randn(8, 512) * 0.05
+    withres = HybridInt4Linear(lin, 128, None, 8, residual_factors=(u, v)).cuda()
+    assert {"res_u", "res_v"} <= set(withres.state_dict())
+    x = torch.randn(3, 512).half().cuda()
+    want = plain(x).float() + (x.float() @ v.half().float().cuda().t()) @ u.half().float().cuda().t()
+    assert (withres(x).float() - want).abs().max() < 5e-3
+    svd = HybridInt4Linear(lin, 128, None, 8, residual_rank=4).cuda()
+    w = lin.weight.detach().cuda()
+    e_plain = (plain(x).float() - x.float() @ w.t()).norm()
+    e_svd = (svd(x).float() - x.float() @ w.t()).norm()
+    assert e_svd < e_plain
+
+
+def test_cuda_graph_capture_and_replay():
+    torch.manual_seed(1)
+    mods = [HybridInt2Linear(nn.Linear(1024, 1024), 128, None, 8, 4).cuda(),
+            HybridInt4Linear(nn.Linear(1024, 1024), 128, None, 8).cuda()]
+    x = torch.randn(1, 1024).half().cuda()
+    eager = mods[1](mods[0](x))
+    static_x = x.clone()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            mods[1](mods[0](static_x))
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = mods[1](mods[0](static_x))
+    g.replay()
+    assert torch.equal(out, eager)
+    x2 = torch.randn(1, 1024).half().cuda()
+    static_x.copy_(x2)
+    g.replay()
+    assert torch.equal(out, mods[1](mods[0](x2)))
+
+
+def test_torch_compile_traces_without_graph_break():
+    torch.manual_seed(2)
+    mod = HybridInt2Linear(nn.Linear(512, 256), 128, None, 4, 2).cuda()
+    mod.graph_safe = True
+    x = torch.randn(2, 512).half().cuda()
+    fn = torch.compile(lambda t: torch.relu(mod(t)) * 2, fullgraph=True)
+    assert torch.equal(fn(x), torch.relu(mod(x)) * 2)
