@@ -125,7 +125,8 @@ extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
         use_mma = plan.ok;
         if (!use_mma && p->kernel == QGEMV_KERNEL_MMA) {
             set_error("qgemv_run: the tensor-core-assisted kernel does not support this shape "
-                      "(needs 16-byte aligned rows and group in {32,64,128,256} for INT4 / {64,128,256} for INT2)");
+                      "(needs 16-byte aligned x and packed rows, group in {32,64,128} for INT4 or {64,128,256} for INT2, "
+                      "at most 256 outlier columns, and M * k_padded small enough for shared memory)");
             return QGEMV_ERR_SHAPE;
         }
     }

@@ -13,13 +13,13 @@ namespace qgemv {
 
 // Workspace layout (bytes from the 256-byte aligned base the caller passes):
 //   [0, 1024)            residual projections t[m][r] = sum_k V[r,k] x[m,k], fp32, QGEMV_MAX_M x 64
-//   [1024, 1024+4*4096)  split-K arrival counters, one int32 per row block (zero between calls)
-//   [WS_PARTIAL_OFF, ..) split-K partial sums, fp32 [splits][M][N]
+//   [1024, 1024+4*16384) arrival counters, one int32 per 16-row tile (zero between calls)
+//   [kWsPartialOff, ..)   partial sums of tiles shared by several warps, fp32 [warp][2][4][32]
 constexpr int    kMaxRank        = 64;
 constexpr size_t kWsTOff         = 0;
 constexpr size_t kWsCounterOff   = 1024;
-constexpr int    kWsMaxCounters  = 4096;
-constexpr size_t kWsPartialOff   = kWsCounterOff + sizeof(int) * kWsMaxCounters;   // 17408, 256-aligned
+constexpr int    kWsMaxCounters  = 16384;          // last entry is the wait-timeout status word
+constexpr size_t kWsPartialOff   = kWsCounterOff + sizeof(int) * kWsMaxCounters;   // 66560, 256-aligned
 constexpr size_t kMaxPartialFloats = size_t(1) << 20;                             // 4 MiB of fp32 partial sums
 
 // Device-side view of one problem; a trivially copyable kernel parameter.
@@ -68,7 +68,16 @@ int launch_residual_t(const Args& a, bool bf16, cudaStream_t s);
 int launch_simt(const Args& a, int bits, bool bf16, int unit_bytes, cudaStream_t s);
 const char* simt_name(int bits, int m, int unit_bytes);
 
-struct MmaPlan { bool ok; int splits; int kspan; int rows_per_cta; const char* name; };
+struct MmaPlan {
+    bool ok;
+    int gb;            // packed bytes per group per row (16, 32 or 64)
+    int nw, stages;    // warps per CTA, ring depth per warp
+    int grid;          // persistent CTAs
+    int nt, nch, ng;   // 16-row tiles, chunks per tile, groups per row
+    int smem_bytes;    // dynamic shared memory
+    int off_xo, off_tt, off_sumx, off_xs, off_ring, off_bar;
+    const char* name;
+};
 MmaPlan plan_mma(const qgemv_problem& p);
 int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& plan, cudaStream_t s);
 
