@@ -5,9 +5,11 @@
 // "unpack + fp32 FMA per weight" loop needs 2 + M instructions per weight and is therefore
 // issue bound (qgemv_simt.cu measures that).  Here the per-weight cost is ~0.6 instructions:
 //
-//  * Packed rows are brought into shared memory by the TMA engine (cp.async.bulk, one copy per
-//    row per chunk, completion on an mbarrier) into a per-warp ring -- no registers, no
-//    coalescing constraints, up to 128 KB in flight per SM.
+//  * Packed rows are brought into a per-warp shared-memory ring with 16-byte asynchronous copies
+//    (cp.async.cg, 256 contiguous bytes per row per chunk) -- no staging registers, rows padded
+//    so that every later shared-memory read is conflict free, ~100 KB in flight per SM.
+//    (One cp.async.bulk per row per chunk was tried first: the TMA engine needed ~110 cycles
+//    per 128-256 byte request per SM, 8x too slow for this access pattern.)
 //  * Codes are NOT converted to numbers.  A 32-bit word is AND-ed with a mask that leaves one
 //    code in the low mantissa bits of each 16-bit half; read as fp16 that is the subnormal
 //    value code * radix^c * 2^-24 (radix = 4 for INT2, 16 for INT4, c = position class).  The
@@ -34,7 +36,6 @@ namespace {
 
 constexpr int kTileRows = 16;          // weight rows per mma tile (one warp owns one tile at a time)
 constexpr int kMaxOutliers = 256;      // outlier activations staged in shared memory
-constexpr int kWaitPollLimit = 1 << 22;
 
 struct MmaArgs {
     Args a;
@@ -44,10 +45,10 @@ struct MmaArgs {
     int row_bytes;     // packed bytes per row actually used (Kpad * bits / 8)
     int nw;            // consumer warps per CTA
     int stages;        // ring depth per warp
-    long long units;   // nt * nch
+    int units;         // nt * nch
     int total_warps;   // warps that own work: min(gridDim.x * nw, units)
     // dynamic shared memory layout (byte offsets)
-    int off_xo, off_tt, off_sumx, off_xs, off_ring, off_bar;
+    int off_xo, off_tt, off_sumx, off_xs, off_ring;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -55,35 +56,19 @@ struct MmaArgs {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+// Asynchronous 16-byte global -> shared copy (LDGSTS), L2-only caching.  Completion is tracked per
+// thread in commit groups; a group counts as done for the whole warp after wait + __syncwarp().
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after kWaitPollLimit polls and reports through *status.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-    for (int i = 0; i < kWaitPollLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(32);
-    }
-    atomicExch(status, 1);
-    return false;
-}
-// TMA engine, untiled form: global -> shared, completion counted in bytes on an mbarrier.
-// Both addresses 16-byte aligned, size a multiple of 16.  No multicast.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
+    if (pending >= 3) cp_async_wait<3>();
+    else if (pending == 2) cp_async_wait<2>();
+    else if (pending == 1) cp_async_wait<1>();
+    else cp_async_wait<0>();
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -96,6 +81,22 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
     return v;
 }
+
+// Optional phase trace (build with -DQGEMV_TRACE): lane 0 of every warp stores the global
+// nanosecond timer at a few points into the upper half of the partial-sum scratch.
+#ifdef QGEMV_TRACE
+#define QTRACE(slot)                                                                            \
+    do {                                                                                        \
+        if ((threadIdx.x & 31) == 0) {                                                          \
+            unsigned long long t_;                                                              \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+            reinterpret_cast<unsigned long long*>(p.a.partial + (kMaxPartialFloats / 2))        \
+                [((size_t)blockIdx.x * 16 + (threadIdx.x >> 5)) * 8 + (slot)] = t_;             \
+        }                                                                                       \
+    } while (0)
+#else
+#define QTRACE(slot) do { } while (0)
+#endif
 
 // Compile-time facts per (bits, group bytes).
 template <int BITS, int GB>
@@ -116,104 +117,141 @@ struct Geo {
 
 
 // ---------------------------------------------------------------------------------------------
-// Activation staging (whole CTA): x -> fp16 multiplicands in B-fragment order, group sums,
-// per-row power-of-two normalisation, outlier activations and residual projections.
+// Activation staging (whole CTA, one pass, one barrier): x -> fp16 multiplicands in B-fragment
+// order, plus per (group, activation row): the offset term and the power-of-two normalisation.
+//
+// One work item = (group, activation row m, quad lane t): the G/4 consecutive activations that
+// lane t of a quad meets in that group.  Items are numbered with (m, t) fastest, which is also
+// the order of the 16-byte fragment slots in shared memory, so a warp's stores are contiguous.
+// The four lanes of an item quad agree on the group's largest magnitude with two shuffles and
+// scale the group so that it sits just below 2^14: fp16 then holds every multiplicand exactly
+// (or with an error far below fp32 rounding for elements 2^-20 times smaller than the largest).
 // ---------------------------------------------------------------------------------------------
-template <int BITS, int GB, int M, bool BF16>
-__device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned char* smem) {
+template <int BITS, int GB, int M, bool BF16, typename AfterLoads>
+__device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned char* smem, AfterLoads after_loads) {
     using XT = typename Act16<BF16>::T;
     using GE = Geo<BITS, GB>;
+    constexpr int EPI = GE::G / 4;          // activations per item
+    constexpr int PPI = EPI / 8;            // 16-byte pieces per item
+    constexpr int WP = GE::CW / 8;          // pieces per 32-bit code word (INT2: 2, INT4: 1)
+    constexpr int RC = PPI <= 4 ? 2 : 1;    // items whose loads one thread keeps in flight together
     const Args& a = p.a;
-    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarp = nthr >> 5;
-    float* hdr = reinterpret_cast<float*>(smem);                      // [0..3] cs[m], [4..7] scratch
-    float* red = reinterpret_cast<float*>(smem) + 8;                   // [nwarp][M] absmax scratch (<= 32*4)
+    const int tid = threadIdx.x, nthr = blockDim.x;
     float* xo = reinterpret_cast<float*>(smem + p.off_xo);
     float* tt = reinterpret_cast<float*>(smem + p.off_tt);
-    float* sumx = reinterpret_cast<float*>(smem + p.off_sumx);
-    __half* xs = reinterpret_cast<__half*>(smem + p.off_xs);
+    float2* gx = reinterpret_cast<float2*>(smem + p.off_sumx);        // {offset term, accumulator scale} per (group, m)
+    uint4* xs16 = reinterpret_cast<uint4*>(smem + p.off_xs);
     const XT* x = static_cast<const XT*>(a.x);
-    const int k8n = a.kpad >> 3;                                       // 16-byte pieces per row of x
+    const int items = p.ng * M * 4;
+    const int span = nthr * RC;
 
-    // pass 1: largest magnitude per activation row
-    float mx[M];
+    uint4 v[RC][PPI];
+    int vg[RC], vm[RC], vt[RC];
+    auto load_items = [&](int base) {
 #pragma unroll
-    for (int m = 0; m < M; ++m) mx[m] = 0.0f;
-    for (int i = tid; i < k8n; i += nthr) {
+        for (int r = 0; r < RC; ++r) {
+            const int item = base + r * nthr + tid;
+            if (item < items) {
+                vt[r] = item & 3;
+                const int gm = item >> 2;
+                vg[r] = gm / M;
+                vm[r] = gm - vg[r] * M;
+                const XT* src = x + (size_t)vm[r] * a.ldx + (size_t)vg[r] * GE::G + vt[r] * EPI;
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + (size_t)i * 8);
-            const XT* e = reinterpret_cast<const XT*>(&v);
+                for (int i = 0; i < PPI; ++i) v[r][i] = reinterpret_cast<const uint4*>(src)[i];
+            } else {
+                vm[r] = -1; vg[r] = 0; vt[r] = 0;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) mx[m] = fmaxf(mx[m], fabsf(Act16<BF16>::to_float(e[q])));
+                for (int i = 0; i < PPI; ++i) v[r][i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+
+    // early loads for the epilogue tables (first round of each held in a register)
+    const int n_xo = a.oc * M, n_tt = a.rank * M;
+    int col0 = -1;
+    if (tid < n_xo) col0 = a.oidx[tid / M];
+    float tt0 = 0.0f;
+    if (tid < n_tt) { const int q = tid / M, m = tid - q * M; tt0 = a.t[m * kMaxRank + q]; }
+    load_items(0);
+    // Every warp's activation loads are queued before any warp starts the bulk weight prefetch
+    // (the barrier waits for the issue of the loads, not for their data).
+    __syncthreads();
+    after_loads();
+    float xo0 = 0.0f;
+    if (tid < n_xo && col0 >= 0 && col0 < a.kpad) xo0 = Act16<BF16>::to_float(x[(size_t)(tid % M) * a.ldx + col0]);
+
+    for (int base = 0; base < items; base += span) {
+        if (base) load_items(base);
+#pragma unroll
+        for (int r = 0; r < RC; ++r) {
+            const bool live = vm[r] >= 0;
+            const int mrow = live ? vm[r] : 0, grp = vg[r], tq = vt[r];
+            float f[EPI];
+            float part = 0.0f, big = 0.0f;
+#pragma unroll
+            for (int i = 0; i < PPI; ++i) {
+                const XT* e = reinterpret_cast<const XT*>(&v[r][i]);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    f[i * 8 + q] = Act16<BF16>::to_float(e[q]);
+                    part += f[i * 8 + q];
+                    big = fmaxf(big, fabsf(f[i * 8 + q]));
+                }
+            }
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, 1));
+            big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, 2));
+            int e2 = 0;
+            if (big > 0.0f && big < 3.0e38f) e2 = (int)((__float_as_uint(big) >> 23) & 0xffu) - 127 - 13;   // floor(log2) - 13
+            e2 = max(-60, min(100, e2));
+            const float down = __int_as_float((127 - e2) << 23);         // 2^-e : multiplier for x
+            const float up = __int_as_float((127 + 24 + e2) << 23);      // 2^(24+e): undoes subnormal unit and group scale
+            if (live) {
+                if (tq == 0) gx[grp * M + mrow] = make_float2(BITS == 2 ? part : 8.0f * part,
+                                                              BITS == 2 ? up * (2.0f / 3.0f) : up);
+#pragma unroll
+                for (int i = 0; i < GE::TW; ++i) {            // one 32-bit code word of this lane
+#pragma unroll
+                    for (int cp = 0; cp < GE::NCLS / 2; ++cp) {
+                        __half2 h2[4];
+#pragma unroll
+                        for (int hh = 0; hh < 8; hh += 2) {
+                            float o[2];
+#pragma unroll
+                            for (int z = 0; z < 2; ++z) {
+                                const int h = hh + z;
+                                const int cl = h >> 2, pp = h & 3;
+                                const int qq = (pp & 1) * 2 + (pp >> 1);
+                                const int c = 2 * cp + cl;
+                                const int j = qq * GE::NCLS + c;                       // code index inside the word
+                                const float sc = __int_as_float((127 - BITS * c) << 23);   // radix^-c
+                                o[z] = f[i * (WP * 8) + j] * down * sc;
+                            }
+                            h2[hh >> 1] = __floats2half2_rn(o[0], o[1]);
+                        }
+                        uint4 outv;
+                        outv.x = *reinterpret_cast<uint32_t*>(&h2[0]); outv.y = *reinterpret_cast<uint32_t*>(&h2[1]);
+                        outv.z = *reinterpret_cast<uint32_t*>(&h2[2]); outv.w = *reinterpret_cast<uint32_t*>(&h2[3]);
+                        xs16[(((size_t)(grp * GE::TW + i) * (GE::NCLS / 2) + cp) * M + mrow) * 4 + tq] = outv;
+                    }
+                }
+            }
         }
     }
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], o));
-        if (lane == 0) red[warp * M + m] = mx[m];
-    }
-    // outlier activations and residual projections for the epilogue
-    for (int i = tid; i < a.oc * M; i += nthr) {
+    if (tid < n_xo) xo[tid] = xo0;
+    if (tid < n_tt) tt[tid] = tt0;
+    for (int i = tid + nthr; i < n_xo; i += nthr) {
         const int j = i / M, m = i - j * M;
         const int col = a.oidx[j];
         xo[i] = (col >= 0 && col < a.kpad) ? Act16<BF16>::to_float(x[(size_t)m * a.ldx + col]) : 0.0f;
     }
-    for (int i = tid; i < a.rank * M; i += nthr) {
+    for (int i = tid + nthr; i < n_tt; i += nthr) {
         const int q = i / M, m = i - q * M;
         tt[i] = a.t[m * kMaxRank + q];
     }
-    __syncthreads();
-    if (tid < M) {
-        float v = 0.0f;
-        for (int w = 0; w < nwarp; ++w) v = fmaxf(v, red[w * M + tid]);
-        int e = 0;
-        if (v > 0.0f && v < 3.0e38f) e = ilogbf(v) - 13;
-        e = max(-60, min(100, e));
-        hdr[4 + tid] = __int_as_float((127 - e) << 23);                 // 2^-e : multiplier for x
-        const float up = __int_as_float((127 + 24 + e) << 23);          // 2^(24+e): undoes subnormal unit and row scale
-        hdr[tid] = BITS == 2 ? up * (2.0f / 3.0f) : up;
-    }
-    __syncthreads();
-
-    // pass 2: scaled multiplicands in fragment order + per-group sums of x
-    constexpr int SEG = GE::G / 8;                                      // lanes that share a group
-    const int total = M * k8n;
-    const int rounds = (total + nthr - 1) / nthr;
-    for (int r = 0; r < rounds; ++r) {
-        const int idx = r * nthr + tid;
-        const bool live = idx < total;
-        const int m = live ? idx / k8n : 0;
-        const int i8 = live ? idx - m * k8n : 0;
-        float part = 0.0f;
-        if (live) {
-            const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + (size_t)i8 * 8);
-            const XT* e = reinterpret_cast<const XT*>(&v);
-            const float down = hdr[4 + m];
-            const int k = i8 * 8;
-            const int grp = k / GE::G, rr = k - grp * GE::G;
-            const int wordpos = rr / GE::CW, t = wordpos / GE::TW, i = wordpos - t * GE::TW;
-            const int j0 = rr - wordpos * GE::CW;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float f = Act16<BF16>::to_float(e[q]);
-                part += f;
-                const int j = j0 + q;
-                const int c = j % GE::NCLS, qq = j / GE::NCLS;
-                const int pos = (qq & 1) * 2 + (qq >> 1);
-                const float sc = __int_as_float((127 - BITS * c) << 23);   // radix^-c
-                const size_t h = ((((size_t)(grp * GE::TW + i) * (GE::NCLS / 2) + (c >> 1)) * M + m) * 4 + t) * 8 +
-                                 (c & 1) * 4 + pos;
-                xs[h] = __float2half_rn(f * down * sc);
-            }
-        }
-#pragma unroll
-        for (int o = 1; o < SEG; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        if (live && (lane % SEG) == 0) {
-            const int grp = (i8 * 8) / GE::G;
-            sumx[grp * M + m] = BITS == 2 ? part : 8.0f * part;
-        }
-    }
+    QTRACE(6);
     __syncthreads();
 }
 
@@ -234,17 +272,43 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
         float e0[M], e1[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) { e0[m] = 0.0f; e1[m] = 0.0f; }
-        for (int j = t; j < a.oc; j += 4) {
-            const float w0 = __half2float(a.ow[(size_t)c0 * a.ldow + j]);
-            const float w1 = __half2float(a.ow[(size_t)c1 * a.ldow + j]);
+        // The four lanes of a quad split the columns; all loads of a batch are issued before use.
+        constexpr int JB = 8;
+        const __half* ow0 = a.ow + (size_t)c0 * a.ldow;
+        const __half* ow1 = a.ow + (size_t)c1 * a.ldow;
+        for (int jb = 0; jb < a.oc; jb += 4 * JB) {
+            __half w0[JB], w1[JB];
 #pragma unroll
-            for (int m = 0; m < M; ++m) { e0[m] = fmaf(w0, xo[j * M + m], e0[m]); e1[m] = fmaf(w1, xo[j * M + m], e1[m]); }
+            for (int i = 0; i < JB; ++i) {
+                const int j = jb + 4 * i + t;
+                w0[i] = j < a.oc ? __ldg(ow0 + j) : __half(0.0f);
+                w1[i] = j < a.oc ? __ldg(ow1 + j) : __half(0.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < JB; ++i) {
+                const int j = min(jb + 4 * i + t, a.oc - 1);
+                const float f0 = __half2float(w0[i]), f1 = __half2float(w1[i]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, xo[j * M + m], e0[m]); e1[m] = fmaf(f1, xo[j * M + m], e1[m]); }
+            }
         }
-        for (int q = t; q < a.rank; q += 4) {
-            const float w0 = __half2float(a.ru[(size_t)c0 * a.ldu + q]);
-            const float w1 = __half2float(a.ru[(size_t)c1 * a.ldu + q]);
+        const __half* ru0 = a.ru + (size_t)c0 * a.ldu;
+        const __half* ru1 = a.ru + (size_t)c1 * a.ldu;
+        for (int qb = 0; qb < a.rank; qb += 4 * JB) {
+            __half w0[JB], w1[JB];
 #pragma unroll
-            for (int m = 0; m < M; ++m) { e0[m] = fmaf(w0, tt[q * M + m], e0[m]); e1[m] = fmaf(w1, tt[q * M + m], e1[m]); }
+            for (int i = 0; i < JB; ++i) {
+                const int q = qb + 4 * i + t;
+                w0[i] = q < a.rank ? __ldg(ru0 + q) : __half(0.0f);
+                w1[i] = q < a.rank ? __ldg(ru1 + q) : __half(0.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < JB; ++i) {
+                const int q = min(qb + 4 * i + t, a.rank - 1);
+                const float f0 = __half2float(w0[i]), f1 = __half2float(w1[i]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, tt[q * M + m], e0[m]); e1[m] = fmaf(f1, tt[q * M + m], e1[m]); }
+            }
         }
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -271,69 +335,72 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
 }
 
 // First unit of warp w, and the warp that owns unit u, under the even split of `units` over `warps`.
-__device__ __forceinline__ long long first_unit(long long w, long long units, long long warps) { return w * units / warps; }
-__device__ __forceinline__ int owner_of(long long u, long long units, long long warps) {
-    return (int)(((u + 1) * warps - 1) / units);
+// (units < 2^31 and warps < 2^16, so the products fit 64 bits; the quotients fit 32.)
+__device__ __forceinline__ int first_unit(int w, int units, int warps) {
+    return (int)((unsigned long long)w * (unsigned)units / (unsigned)warps);
+}
+__device__ __forceinline__ int owner_of(int u, int units, int warps) {
+    return (int)((((unsigned long long)u + 1) * (unsigned)warps - 1) / (unsigned)units);
 }
 
 // ---------------------------------------------------------------------------------------------
 // The kernel.  blockDim.x = 32 * nw; every warp is its own producer and consumer.
 // ---------------------------------------------------------------------------------------------
 template <int BITS, int GB, int M, bool BF16>
-__global__ void __launch_bounds__(256, 1) qgemv_mma_kernel(const __grid_constant__ MmaArgs p) {
+__global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant__ MmaArgs p) {
     using GE = Geo<BITS, GB>;
     extern __shared__ __align__(128) unsigned char smem[];
     const Args& a = p.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     // Global warp index, CTA-minor, so that the first W warps are spread over all CTAs.  W never
     // exceeds the number of units: every warp below W owns at least one unit, the rest idle.
-    const long long W = p.total_warps;
-    const long long gw = (long long)warp * gridDim.x + blockIdx.x;
+    const int W = p.total_warps, U = p.units;
+    const int gw = warp * gridDim.x + blockIdx.x;
     const bool active = gw < W;
-    const long long u0 = active ? first_unit(gw, p.units, W) : 0, u1 = active ? first_unit(gw + 1, p.units, W) : 0;
-    int* status = a.counters + (kWsMaxCounters - 1);
+    const int u0 = active ? first_unit(gw, U, W) : 0, u1 = active ? first_unit(gw + 1, U, W) : 0;
 
     unsigned char* ring = smem + p.off_ring + (size_t)warp * p.stages * GE::STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring);
-    const uint32_t bar_u32 = smem_u32(smem + p.off_bar) + warp * p.stages * 8;
+    QTRACE(0);
 
-    if (lane == 0) {
-        for (int s = 0; s < p.stages; ++s) mbar_init(bar_u32 + s * 8, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncwarp();
-
-    // Start the copy of unit u into ring slot s (all lanes call; lanes 0..15 each move one row).
-    auto issue = [&](long long u, int s) {
-        const int tile = (int)(u / p.nch), ch = (int)(u - (long long)tile * p.nch);
-        const uint32_t bytes = (uint32_t)min(GE::CB, p.row_bytes - ch * GE::CB);
-        const uint32_t bar = bar_u32 + s * 8;
-        if (lane == 0) mbar_expect_tx(bar, bytes * kTileRows);
-        __syncwarp();
-        if (lane < kTileRows) {
-            const int row = min(tile * kTileRows + lane, a.n - 1);
-            bulk_g2s(ring_u32 + s * GE::STAGE_BYTES + lane * GE::PITCH,
-                     a.packed + (size_t)row * a.ldp + (size_t)ch * GE::CB, bytes, bar);
+    // Start the copy of the unit (tile, ch) into ring slot s and commit it as one group (every lane
+    // commits exactly one group per call, empty or not, so the group arithmetic stays uniform).
+    constexpr int PPR = GE::CB / 16;                 // 16-byte pieces per row of a full chunk
+    constexpr int RPI = 32 / PPR;                    // rows covered by one warp-wide copy instruction
+    const int lrow = lane / PPR, lcol = lane % PPR;
+    auto issue = [&](bool valid, int tile, int ch, int s) {
+        if (valid) {
+            const int pieces = min(GE::CB, p.row_bytes - ch * GE::CB) >> 4;
+            if (lcol < pieces) {
+                const uint32_t dst = ring_u32 + s * GE::STAGE_BYTES + lcol * 16;
+                const uint8_t* src = a.packed + (size_t)ch * GE::CB + lcol * 16;
+#pragma unroll
+                for (int it = 0; it < kTileRows / RPI; ++it) {
+                    const int r = it * RPI + lrow;
+                    const int row = min(tile * kTileRows + r, a.n - 1);
+                    cp_async16(dst + r * GE::PITCH, src + (size_t)row * a.ldp);
+                }
+            }
         }
+        cp_async_commit();
     };
 
-    long long pf = u0;
-    for (int s = 0; s < p.stages; ++s, ++pf)
-        if (pf < u1) issue(pf, s);
+    // prefetch cursor (pf_*) runs `stages` units ahead of the consume cursor
+    int pf = u0, pf_tile = u0 / p.nch, pf_ch = u0 - pf_tile * p.nch;
+    auto advance_pf = [&]() { ++pf; if (++pf_ch == p.nch) { pf_ch = 0; ++pf_tile; } };
+    stage_activations<BITS, GB, M, BF16>(p, smem, [&]() {
+        for (int s = 0; s < p.stages; ++s) { issue(pf < u1, pf_tile, pf_ch, s); advance_pf(); }
+        QTRACE(1);
+    });                                                   // CTA-wide, ends with __syncthreads()
+    QTRACE(2);
 
-    stage_activations<BITS, GB, M, BF16>(p, smem);       // CTA-wide, ends with __syncthreads()
-
-    const float* hdr = reinterpret_cast<const float*>(smem);
-    const float* sumx = reinterpret_cast<const float*>(smem + p.off_sumx);
+    const float2* gx = reinterpret_cast<const float2*>(smem + p.off_sumx);
     const uint4* xs16 = reinterpret_cast<const uint4*>(smem + p.off_xs);
     const int ma = min(2 * t, M - 1), mb = min(2 * t + 1, M - 1);
-    const float csa = hdr[ma], csb = hdr[mb];
 
-    // scales of the current unit (raw fp16), one per (row g / g+8, group of the chunk)
+    // scales of a unit (raw fp16), one per (row g / g+8, group of the chunk), fetched one unit ahead
     __half sc0[GE::CG], sc1[GE::CG];
-    auto load_scales = [&](long long u, __half (&d0)[GE::CG], __half (&d1)[GE::CG]) {
-        const int tile = (int)(u / p.nch), ch = (int)(u - (long long)tile * p.nch);
+    auto load_scales = [&](int tile, int ch, __half (&d0)[GE::CG], __half (&d1)[GE::CG]) {
         const int ra = min(tile * kTileRows + g, a.n - 1), rb = min(tile * kTileRows + g + 8, a.n - 1);
         const __half* pa = a.scales + (size_t)ra * a.lds + ch * GE::CG;
         const __half* pb = a.scales + (size_t)rb * a.lds + ch * GE::CG;
@@ -344,23 +411,23 @@ __global__ void __launch_bounds__(256, 1) qgemv_mma_kernel(const __grid_constant
             d1[i] = i < ngr ? __ldg(pb + i) : __half(0.0f);
         }
     };
-    if (u0 < u1) load_scales(u0, sc0, sc1);
+    int tile = u0 / p.nch, ch = u0 - tile * p.nch;
+    const int my_first_tile = tile;
+    if (u0 < u1) load_scales(tile, ch, sc0, sc1);
 
     float y[4] = {0.f, 0.f, 0.f, 0.f};
-    int seg_first_ch = 0, cur_tile = -1;
-    const int my_first_tile = (int)(u0 / p.nch);
-    uint32_t phases = 0;
+    int seg_first_ch = ch;
     int stage = 0;
-    bool healthy = true;
 
-    for (long long u = u0; u < u1; ++u) {
-        const int tile = (int)(u / p.nch), ch = (int)(u - (long long)tile * p.nch);
-        if (tile != cur_tile) { cur_tile = tile; seg_first_ch = ch; y[0] = y[1] = y[2] = y[3] = 0.f; }
+    for (int u = u0; u < u1; ++u) {
+        int ntile = tile, nch_ = ch + 1;
+        if (nch_ == p.nch) { nch_ = 0; ++ntile; }
         __half nsc0[GE::CG], nsc1[GE::CG];
-        if (u + 1 < u1) load_scales(u + 1, nsc0, nsc1);
+        if (u + 1 < u1) load_scales(ntile, nch_, nsc0, nsc1);
 
-        if (healthy) healthy = mbar_wait(bar_u32 + stage * 8, (phases >> stage) & 1u, status);
-        phases ^= 1u << stage;
+        cp_async_wait_dyn(p.stages - 1);        // all but the newest stages-1 groups are done: unit u has landed
+        __syncwarp();
+        if (u == u0) QTRACE(3);
         const int ngr = min(GE::CG, p.ng - ch * GE::CG);
         const unsigned char* base0 = ring + stage * GE::STAGE_BYTES + g * GE::PITCH + t * GE::TB;
         const unsigned char* base1 = base0 + 8 * GE::PITCH;
@@ -382,35 +449,38 @@ __global__ void __launch_bounds__(256, 1) qgemv_mma_kernel(const __grid_constant
                     w0[0] = v0.x; w0[1] = v0.y; w0[2] = v0.z; w0[3] = v0.w;
                     w1[0] = v1.x; w1[1] = v1.y; w1[2] = v1.z; w1[3] = v1.w;
                 }
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                // two independent accumulator chains (the classes alternate between them)
+                float accA[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint4* xg = xs16 + ((size_t)(G * GE::TW) * (GE::NCLS / 2) * M + g) * 4 + t;
 #pragma unroll
                 for (int i = 0; i < GE::TW; ++i) {
                     const uint32_t h0 = w0[i] >> 8, h1 = w1[i] >> 8;
 #pragma unroll
                     for (int cp = 0; cp < GE::NCLS / 2; ++cp) {
                         uint4 b = make_uint4(0u, 0u, 0u, 0u);
-                        if (g < M) b = xs16[(((size_t)(G * GE::TW + i) * (GE::NCLS / 2) + cp) * M + g) * 4 + t];
+                        if (g < M) b = xg[(size_t)(i * (GE::NCLS / 2) + cp) * M * 4];
                         constexpr uint32_t MK = GE::MASK;
                         const uint32_t m0 = MK << (BITS * (2 * cp)), m1 = MK << (BITS * (2 * cp + 1));
-                        mma_f16(acc, w0[i] & m0, w1[i] & m0, h0 & m0, h1 & m0, b.x, b.y);
-                        mma_f16(acc, w0[i] & m1, w1[i] & m1, h0 & m1, h1 & m1, b.z, b.w);
+                        mma_f16(accA, w0[i] & m0, w1[i] & m0, h0 & m0, h1 & m0, b.x, b.y);
+                        mma_f16(accB, w0[i] & m1, w1[i] & m1, h0 & m1, h1 & m1, b.z, b.w);
                     }
                 }
                 const float s0 = __half2float(sc0[gi]), s1 = __half2float(sc1[gi]);
-                const float xa = sumx[G * M + ma], xb = sumx[G * M + mb];
-                y[0] = fmaf(s0, fmaf(csa, acc[0], -xa), y[0]);
-                y[1] = fmaf(s0, fmaf(csb, acc[1], -xb), y[1]);
-                y[2] = fmaf(s1, fmaf(csa, acc[2], -xa), y[2]);
-                y[3] = fmaf(s1, fmaf(csb, acc[3], -xb), y[3]);
+                const float2 ga = gx[G * M + ma], gb = gx[G * M + mb];
+                y[0] = fmaf(s0, fmaf(ga.y, accA[0] + accB[0], -ga.x), y[0]);
+                y[1] = fmaf(s0, fmaf(gb.y, accA[1] + accB[1], -gb.x), y[1]);
+                y[2] = fmaf(s1, fmaf(ga.y, accA[2] + accB[2], -ga.x), y[2]);
+                y[3] = fmaf(s1, fmaf(gb.y, accA[3] + accB[3], -gb.x), y[3]);
             }
         }
         __syncwarp();
-        if (pf < u1) issue(pf, stage);
-        ++pf;
+        issue(pf < u1, pf_tile, pf_ch, stage);
+        advance_pf();
         stage = stage + 1 == p.stages ? 0 : stage + 1;
 #pragma unroll
         for (int i = 0; i < GE::CG; ++i) { sc0[i] = nsc0[i]; sc1[i] = nsc1[i]; }
 
+        if (u == u1 - 1) QTRACE(4);
         if (ch == p.nch - 1 || u == u1 - 1) {
             if (seg_first_ch == 0 && ch == p.nch - 1) {
                 finish_tile<M, BF16>(p, smem, tile, y);
@@ -422,8 +492,8 @@ __global__ void __launch_bounds__(256, 1) qgemv_mma_kernel(const __grid_constant
                 for (int i = 0; i < 4; ++i) mine[i * 32 + lane] = y[i];
                 __threadfence();
                 __syncwarp();
-                const int wf = owner_of((long long)tile * p.nch, p.units, W);
-                const int wl = owner_of((long long)tile * p.nch + p.nch - 1, p.units, W);
+                const int wf = owner_of(tile * p.nch, U, W);
+                const int wl = owner_of(tile * p.nch + p.nch - 1, U, W);
                 int last = 0;
                 if (lane == 0) {
                     const int old = atomicAdd(&a.counters[tile], 1);
@@ -434,17 +504,32 @@ __global__ void __launch_bounds__(256, 1) qgemv_mma_kernel(const __grid_constant
                 if (last) {
                     __threadfence();
                     y[0] = y[1] = y[2] = y[3] = 0.f;
-                    for (int w = wf; w <= wl; ++w) {
-                        const int s = tile == (int)(first_unit(w, p.units, W) / p.nch) ? 0 : 1;
-                        const float* src = a.partial + ((size_t)(w * 2 + s) * 4) * 32;
+                    for (int wb = wf; wb <= wl; wb += 4) {     // four contributors' loads in flight at a time
+                        float v[4][4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) y[i] += ld_cg_f32(src + i * 32 + lane);
+                        for (int k = 0; k < 4; ++k) {
+                            const int w = min(wb + k, wl);
+                            const int s = tile == first_unit(w, U, W) / p.nch ? 0 : 1;
+                            const float* src = a.partial + ((size_t)(w * 2 + s) * 4) * 32;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[k][i] = ld_cg_f32(src + i * 32 + lane);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (wb + k <= wl) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) y[i] += v[k][i];
+                            }
                     }
                     finish_tile<M, BF16>(p, smem, tile, y);
                 }
             }
+            y[0] = y[1] = y[2] = y[3] = 0.f;
+            seg_first_ch = 0;
         }
+        tile = ntile; ch = nch_;
     }
+    QTRACE(5);
 }
 
 constexpr int kMaxDynSmem = 232448;   // 227 KB per CTA on sm_100
@@ -520,21 +605,22 @@ MmaPlan plan_mma(const qgemv_problem& p) {
     int off = 1024;
     pl.off_xo = off;   off = align_up(off + p.outliers * p.m * 4, 16);
     pl.off_tt = off;   off = align_up(off + p.rank * p.m * 4, 16);
-    pl.off_sumx = off; off = align_up(off + pl.ng * p.m * 4, 16);
+    pl.off_sumx = off; off = align_up(off + pl.ng * p.m * 8, 16);
     pl.off_xs = off;   off = align_up(off + p.m * p.k_padded * 2, 128);
     pl.off_ring = off;
-    int nw = 8, stages = 0;
-    for (; nw >= 4; nw -= 4) {
-        const int avail = kMaxDynSmem - off - nw * 4 * 8 - 64;
-        stages = avail / (nw * stage_bytes);
-        if (stages > 4) stages = 4;
-        if (stages >= 2) break;
-    }
-    if (stages < 2) return pl;
+    // Most warps first (latency hiding), at least 3 ring slots each if possible.
+    int nw = 0, stages = 0;
+    const int avail = kMaxDynSmem - off;
+    for (int want = 3; want >= 2 && !nw; --want)
+        for (int cand = 16; cand >= 4; cand -= 4)
+            if (avail / (cand * stage_bytes) >= want) { nw = cand; stages = avail / (cand * stage_bytes); break; }
+    if (!nw) return pl;
+    if (stages > 4) stages = 4;
+    if ((long long)pl.nt * pl.nch > 0x3fffffff) return pl;
     pl.nw = nw;
     pl.stages = stages;
-    pl.off_bar = align_up(off + nw * stages * stage_bytes, 16);
-    pl.smem_bytes = pl.off_bar + nw * stages * 8;
+    pl.off_bar = 0;
+    pl.smem_bytes = off + nw * stages * stage_bytes;
     const long long units = (long long)pl.nt * pl.nch;
     const int sms = sm_count();
     pl.grid = (int)(units < sms ? units : sms);
@@ -552,10 +638,10 @@ int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, cudaStream
     p.nt = pl.nt; p.nch = pl.nch; p.ng = pl.ng;
     p.row_bytes = a.kpad * bits / 8;
     p.nw = pl.nw; p.stages = pl.stages;
-    p.units = (long long)pl.nt * pl.nch;
-    p.total_warps = (int)(p.units < (long long)pl.grid * pl.nw ? p.units : (long long)pl.grid * pl.nw);
+    p.units = pl.nt * pl.nch;
+    p.total_warps = p.units < pl.grid * pl.nw ? p.units : pl.grid * pl.nw;
     p.off_xo = pl.off_xo; p.off_tt = pl.off_tt; p.off_sumx = pl.off_sumx; p.off_xs = pl.off_xs;
-    p.off_ring = pl.off_ring; p.off_bar = pl.off_bar;
+    p.off_ring = pl.off_ring;
     return bits == 2 ? launch_gb<2>(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s)
                      : launch_gb<4>(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s);
 }
