@@ -70,12 +70,15 @@ const char* simt_name(int bits, int m, int unit_bytes);
 
 struct MmaPlan {
     bool ok;
-    int gb;            // packed bytes per group per row (16, 32 or 64)
-    int nw, stages;    // warps per CTA, ring depth per warp
-    int grid;          // persistent CTAs
-    int nt, nch, ng;   // 16-row tiles, chunks per tile, groups per row
-    int smem_bytes;    // dynamic shared memory
-    int off_xo, off_tt, off_sumx, off_xs, off_ring, off_bar;
+    int gb;                 // packed bytes per group per row (16, 32 or 64)
+    int nw, stages;         // warps per CTA, ring depth per warp
+    int grid;               // persistent CTAs
+    int nt, nch, ng;        // 16-row tiles, chunks per tile, groups per row
+    int rlen, rpt;          // chunks per run, runs per tile
+    int tile_aligned;       // CTAs own whole tiles
+    int scales_async, epi_async, ocb, rb, epi_bytes;
+    int smem_bytes;         // dynamic shared memory
+    int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
     const char* name;
 };
 MmaPlan plan_mma(const qgemv_problem& p);

@@ -21,10 +21,16 @@
 //    dot product sum(code * x) per group, scaled by a power of two.
 //  * Per group the fp32 partial sum is combined with the group scale and the level offset
 //    (INT2: level = (2c-3)/3, INT4: level = c-8) using the pre-computed sum of x over the group.
-//  * Work is split stream-K style: the (16-row tile, K-chunk) units are dealt out evenly to
-//    all warps of a persistent grid, so every SM gets the same number of bytes whatever N and
-//    K are.  A tile finished by one warp goes straight to the epilogue; a tile shared by several
-//    warps is summed, in fixed order, by whichever warp arrives last (no waiting, deterministic).
+//  * Work is split stream-K style: the (16-row tile, K-run) units are dealt out evenly to the
+//    CTAs of a persistent grid (one per SM), so every SM gets the same number of bytes whatever
+//    N and K are; inside a CTA the warps pull runs from a shared-memory queue.  Partial sums of
+//    a tile meet in shared memory and are added in fixed order.  Only the (at most two) tiles a
+//    CTA shares with its neighbours go through global memory, where whichever CTA arrives last
+//    adds the contributions in CTA order (no waiting, deterministic).
+//  * Everything the kernel needs from DRAM rides the same asynchronous stream as the codes: the
+//    group scales sit in the ring beside their chunk, the outlier / residual rows of a warp's
+//    first tile are prefetched at kernel start.  A plain load issued while ~100 KB per SM of
+//    prefetch is queued would wait behind all of it.
 //  * Epilogue in the same kernel: exact fp16 outlier columns, rank-r residual, bias, activation.
 //
 // Replaces _decode_gemv (ai_accel_lab/kernels/decode_int2.py:43-96) and _decode_int4_gemv
@@ -43,12 +49,19 @@ struct MmaArgs {
     int nch;           // chunks per tile
     int ng;            // groups per row
     int row_bytes;     // packed bytes per row actually used (Kpad * bits / 8)
-    int nw;            // consumer warps per CTA
+    int nw;            // warps per CTA
     int stages;        // ring depth per warp
-    int units;         // nt * nch
-    int total_warps;   // warps that own work: min(gridDim.x * nw, units)
+    int rlen;          // chunks per run (a run = consecutive chunks of one tile, the unit of work)
+    int rpt;           // runs per tile
+    int runs;          // nt * rpt
+    int scales_async;  // scale rows are aligned for 8/16-byte asynchronous copies
+    int epi_async;     // outlier / residual rows are aligned for 16-byte asynchronous copies
+    int ocb, rb;       // bytes per prefetched outlier-weight row / residual row (multiples of 16)
+    int epi_bytes;     // bytes of one warp's epilogue prefetch buffer
+    int wait_for_x;    // 1: the producer of x may still be running when this kernel starts
+    int tile_aligned;  // 1: every CTA owns whole tiles
     // dynamic shared memory layout (byte offsets)
-    int off_xo, off_tt, off_sumx, off_xs, off_ring;
+    int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -60,6 +73,12 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 // thread in commit groups; a group counts as done for the whole warp after wait + __syncwarp().
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING>
@@ -76,6 +95,10 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// Programmatic dependent launch: let the next kernel in the stream begin its prologue now, and
+// block until the kernels this one depends on have completed and flushed their writes.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -107,10 +130,17 @@ struct Geo {
     static constexpr int G = GB * CPB;                   // group size in codes
     static constexpr int TB = GB / 4;                    // bytes one lane reads per row per group
     static constexpr int TW = TB / 4;                    // ... in 32-bit words
-    static constexpr int CG = (256 / GB) > 8 ? 8 : (256 / GB);   // groups per chunk
-    static constexpr int CB = CG * GB;                   // chunk bytes per row (128 or 256)
-    static constexpr int PITCH = CB + GB;                // shared-memory row pitch: conflict-free for TB-wide reads
-    static constexpr int STAGE_BYTES = kTileRows * PITCH;
+    static constexpr int CB = 128;                       // chunk bytes per row: one 128-byte line
+    static constexpr int CG = CB / GB;                   // groups per chunk (8, 4 or 2)
+    static constexpr int PITCH = CB;                     // rows are dense in shared memory ...
+    // ... and bank conflicts are avoided by storing 16-byte piece c of row r at piece position
+    // c ^ swz(r): the rows a shared-memory instruction touches together (2 for 16-byte reads,
+    // 4 for 8-byte, 8 for 4-byte reads) land in different 128/R-byte bank groups.
+    static constexpr int SWZ_ROWS = 128 / (4 * TB);      // R: 2, 4 or 8
+    static constexpr int SWZ_MUL = 8 / SWZ_ROWS;
+    static __device__ __forceinline__ int swz(int row) { return (row % SWZ_ROWS) * SWZ_MUL; }
+    static constexpr int SCALE_OFF = kTileRows * PITCH;  // 16 bytes of scales per row follow the codes
+    static constexpr int STAGE_BYTES = kTileRows * PITCH + kTileRows * 16;
     static constexpr uint32_t MASK = BITS == 2 ? 0x00030003u : 0x000f000fu;
     // halves of x' per group laid out for the B fragments: [TW][NCLS/2][M][4 lanes t][8 halves]
 };
@@ -138,8 +168,7 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
     const Args& a = p.a;
     const int tid = threadIdx.x, nthr = blockDim.x;
     float* xo = reinterpret_cast<float*>(smem + p.off_xo);
-    float* tt = reinterpret_cast<float*>(smem + p.off_tt);
-    float2* gx = reinterpret_cast<float2*>(smem + p.off_sumx);        // {offset term, accumulator scale} per (group, m)
+    float2* gx = reinterpret_cast<float2*>(smem + p.off_gx);          // {offset term, accumulator scale} per (group, m)
     uint4* xs16 = reinterpret_cast<uint4*>(smem + p.off_xs);
     const XT* x = static_cast<const XT*>(a.x);
     const int items = p.ng * M * 4;
@@ -167,19 +196,15 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
         }
     };
 
-    // early loads for the epilogue tables (first round of each held in a register)
-    const int n_xo = a.oc * M, n_tt = a.rank * M;
+    // outlier column indices (static data): first round held in a register
+    const int n_xo = a.oc * M;
     int col0 = -1;
     if (tid < n_xo) col0 = a.oidx[tid / M];
-    float tt0 = 0.0f;
-    if (tid < n_tt) { const int q = tid / M, m = tid - q * M; tt0 = a.t[m * kMaxRank + q]; }
     load_items(0);
     // Every warp's activation loads are queued before any warp starts the bulk weight prefetch
     // (the barrier waits for the issue of the loads, not for their data).
     __syncthreads();
     after_loads();
-    float xo0 = 0.0f;
-    if (tid < n_xo && col0 >= 0 && col0 < a.kpad) xo0 = Act16<BF16>::to_float(x[(size_t)(tid % M) * a.ldx + col0]);
 
     for (int base = 0; base < items; base += span) {
         if (base) load_items(base);
@@ -240,27 +265,40 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
             }
         }
     }
-    if (tid < n_xo) xo[tid] = xo0;
-    if (tid < n_tt) tt[tid] = tt0;
-    for (int i = tid + nthr; i < n_xo; i += nthr) {
+    __syncthreads();
+    // Outlier activations, read back from the staged multiplicands (no further global loads of x:
+    // they would queue behind the weight stream).  x[m][col] = staged * radix^c * 2^e(group).
+    const __half* xs = reinterpret_cast<const __half*>(smem + p.off_xs);
+    for (int i = tid; i < n_xo; i += nthr) {
         const int j = i / M, m = i - j * M;
-        const int col = a.oidx[j];
-        xo[i] = (col >= 0 && col < a.kpad) ? Act16<BF16>::to_float(x[(size_t)m * a.ldx + col]) : 0.0f;
-    }
-    for (int i = tid + nthr; i < n_tt; i += nthr) {
-        const int q = i / M, m = i - q * M;
-        tt[i] = a.t[m * kMaxRank + q];
+        const int col = i < nthr ? col0 : a.oidx[j];
+        float val = 0.0f;
+        if (col >= 0 && col < a.kpad) {
+            const int grp = col / GE::G, rr = col - grp * GE::G;
+            const int wordpos = rr / GE::CW, t = wordpos / GE::TW, ii = wordpos - t * GE::TW;
+            const int jj = rr - wordpos * GE::CW;
+            const int c = jj % GE::NCLS, qq = jj / GE::NCLS;
+            const int pos = (qq & 1) * 2 + (qq >> 1);
+            const size_t h = ((((size_t)(grp * GE::TW + ii) * (GE::NCLS / 2) + (c >> 1)) * M + m) * 4 + t) * 8 +
+                             (c & 1) * 4 + pos;
+            const float up = gx[grp * M + m].y * (BITS == 2 ? 1.5f : 1.0f);      // 2^(24 + e)
+            val = __half2float(xs[h]) * __int_as_float((127 - 24 + BITS * c) << 23) * up;
+        }
+        xo[i] = val;
     }
     QTRACE(6);
-    __syncthreads();
+    // no barrier here: the table is first read after the CTA-wide barrier that ends the main loop
 }
 
 // ---------------------------------------------------------------------------------------------
 // Epilogue of one finished 16-row tile: outlier columns, residual, bias, activation, store.
 // Lane (g = lane/4, t = lane%4) holds rows tile*16+g and +8, activation rows 2t and 2t+1.
+// `pre` points at this warp's prefetched copy of the tile's outlier-weight rows, residual rows
+// and bias (shared memory), or is null, in which case they are read from global memory.
 // ---------------------------------------------------------------------------------------------
 template <int M, bool BF16>
-__device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned char* smem, int tile, float (&y)[4]) {
+__device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned char* smem, int tile, float (&y)[4],
+                                            const unsigned char* pre) {
     using XT = typename Act16<BF16>::T;
     const Args& a = p.a;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -268,21 +306,20 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
     const int c0 = min(r0, a.n - 1), c1 = min(r1, a.n - 1);
     if (a.oc > 0 || a.rank > 0) {
         const float* xo = reinterpret_cast<const float*>(smem + p.off_xo);
-        const float* tt = reinterpret_cast<const float*>(smem + p.off_tt);
         float e0[M], e1[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) { e0[m] = 0.0f; e1[m] = 0.0f; }
         // The four lanes of a quad split the columns; all loads of a batch are issued before use.
         constexpr int JB = 8;
-        const __half* ow0 = a.ow + (size_t)c0 * a.ldow;
-        const __half* ow1 = a.ow + (size_t)c1 * a.ldow;
+        const __half* ow0 = pre ? reinterpret_cast<const __half*>(pre + g * p.ocb) : a.ow + (size_t)c0 * a.ldow;
+        const __half* ow1 = pre ? reinterpret_cast<const __half*>(pre + (g + 8) * p.ocb) : a.ow + (size_t)c1 * a.ldow;
         for (int jb = 0; jb < a.oc; jb += 4 * JB) {
             __half w0[JB], w1[JB];
 #pragma unroll
             for (int i = 0; i < JB; ++i) {
                 const int j = jb + 4 * i + t;
-                w0[i] = j < a.oc ? __ldg(ow0 + j) : __half(0.0f);
-                w1[i] = j < a.oc ? __ldg(ow1 + j) : __half(0.0f);
+                w0[i] = j < a.oc ? ow0[j] : __half(0.0f);
+                w1[i] = j < a.oc ? ow1[j] : __half(0.0f);
             }
 #pragma unroll
             for (int i = 0; i < JB; ++i) {
@@ -292,22 +329,27 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
                 for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, xo[j * M + m], e0[m]); e1[m] = fmaf(f1, xo[j * M + m], e1[m]); }
             }
         }
-        const __half* ru0 = a.ru + (size_t)c0 * a.ldu;
-        const __half* ru1 = a.ru + (size_t)c1 * a.ldu;
+        const unsigned char* preu = pre ? pre + kTileRows * p.ocb : nullptr;
+        const __half* ru0 = pre ? reinterpret_cast<const __half*>(preu + g * p.rb) : a.ru + (size_t)c0 * a.ldu;
+        const __half* ru1 = pre ? reinterpret_cast<const __half*>(preu + (g + 8) * p.rb) : a.ru + (size_t)c1 * a.ldu;
+        if (a.rank > 0) pdl_wait();            // the residual projections come from the kernel launched just before
         for (int qb = 0; qb < a.rank; qb += 4 * JB) {
             __half w0[JB], w1[JB];
+            float tq[JB][M];
 #pragma unroll
             for (int i = 0; i < JB; ++i) {
                 const int q = qb + 4 * i + t;
-                w0[i] = q < a.rank ? __ldg(ru0 + q) : __half(0.0f);
-                w1[i] = q < a.rank ? __ldg(ru1 + q) : __half(0.0f);
+                w0[i] = q < a.rank ? ru0[q] : __half(0.0f);
+                w1[i] = q < a.rank ? ru1[q] : __half(0.0f);
+                const int qc = min(q, a.rank - 1);
+#pragma unroll
+                for (int m = 0; m < M; ++m) tq[i][m] = ld_cg_f32(a.t + m * kMaxRank + qc);
             }
 #pragma unroll
             for (int i = 0; i < JB; ++i) {
-                const int q = min(qb + 4 * i + t, a.rank - 1);
                 const float f0 = __half2float(w0[i]), f1 = __half2float(w1[i]);
 #pragma unroll
-                for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, tt[q * M + m], e0[m]); e1[m] = fmaf(f1, tt[q * M + m], e1[m]); }
+                for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, tq[i][m], e0[m]); e1[m] = fmaf(f1, tq[i][m], e1[m]); }
             }
         }
 #pragma unroll
@@ -322,8 +364,15 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
         }
     }
     XT* out = static_cast<XT*>(a.y);
-    const float b0 = a.bias ? __half2float(a.bias[c0]) : 0.0f;
-    const float b1 = a.bias ? __half2float(a.bias[c1]) : 0.0f;
+    float b0 = 0.0f, b1 = 0.0f;
+    if (a.bias) {
+        if (pre) {
+            const __half* pb = reinterpret_cast<const __half*>(pre + kTileRows * (p.ocb + p.rb));
+            b0 = __half2float(pb[g]); b1 = __half2float(pb[g + 8]);
+        } else {
+            b0 = __half2float(a.bias[c0]); b1 = __half2float(a.bias[c1]);
+        }
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int m = 2 * t + h;
@@ -334,131 +383,227 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
     }
 }
 
-// First unit of warp w, and the warp that owns unit u, under the even split of `units` over `warps`.
-// (units < 2^31 and warps < 2^16, so the products fit 64 bits; the quotients fit 32.)
-__device__ __forceinline__ int first_unit(int w, int units, int warps) {
-    return (int)((unsigned long long)w * (unsigned)units / (unsigned)warps);
+// First unit of part w, and the part that owns unit u, under the even split of `units` over `parts`
+// (units >= parts, so no part is empty; units < 2^31 and parts < 2^16, so the products fit 64 bits).
+__device__ __forceinline__ int first_unit(int w, int units, int parts) {
+    return (int)((unsigned long long)w * (unsigned)units / (unsigned)parts);
 }
-__device__ __forceinline__ int owner_of(int u, int units, int warps) {
-    return (int)((((unsigned long long)u + 1) * (unsigned)warps - 1) / (unsigned)units);
+__device__ __forceinline__ int owner_of(int u, int units, int parts) {
+    return (int)((((unsigned long long)u + 1) * (unsigned)parts - 1) / (unsigned)units);
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel.  blockDim.x = 32 * nw; every warp is its own producer and consumer.
+// The kernel.  Persistent grid, blockDim.x = 32 * nw; every warp is its own producer and consumer.
 // ---------------------------------------------------------------------------------------------
 template <int BITS, int GB, int M, bool BF16>
 __global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant__ MmaArgs p) {
     using GE = Geo<BITS, GB>;
+    constexpr int TT = (M + 1) / 2;                   // quad lanes that hold useful output columns
+    constexpr int SLOT_BYTES = 8 * TT * 16;           // one run's partial sums in shared memory
     extern __shared__ __align__(128) unsigned char smem[];
     const Args& a = p.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    // Global warp index, CTA-minor, so that the first W warps are spread over all CTAs.  W never
-    // exceeds the number of units: every warp below W owns at least one unit, the rest idle.
-    const int W = p.total_warps, U = p.units;
-    const int gw = warp * gridDim.x + blockIdx.x;
-    const bool active = gw < W;
-    const int u0 = active ? first_unit(gw, U, W) : 0, u1 = active ? first_unit(gw + 1, U, W) : 0;
+    pdl_launch_dependents();
+    if (p.wait_for_x) pdl_wait();
+
+    // This CTA's share of the runs, and the tiles they touch.
+    const int grid = gridDim.x, cta = blockIdx.x;
+    // Whole tiles per CTA when that balances well enough (no tile is then shared between CTAs),
+    // otherwise an even split of the runs.
+    const int r0 = p.tile_aligned ? first_unit(cta, p.nt, grid) * p.rpt : first_unit(cta, p.runs, grid);
+    const int r1 = p.tile_aligned ? first_unit(cta + 1, p.nt, grid) * p.rpt : first_unit(cta + 1, p.runs, grid);
+    const int T0 = r0 / p.rpt, T1 = (r1 - 1) / p.rpt;
 
     unsigned char* ring = smem + p.off_ring + (size_t)warp * p.stages * GE::STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring);
+    int4* meta = reinterpret_cast<int4*>(smem + p.off_meta) + warp * 4;      // per stage: tile, chunk, slot, last
+    unsigned char* epi = smem + p.off_epi + (size_t)warp * p.epi_bytes;
     QTRACE(0);
 
-    // Start the copy of the unit (tile, ch) into ring slot s and commit it as one group (every lane
-    // commits exactly one group per call, empty or not, so the group arithmetic stays uniform).
+    // ---- producer side: pull runs from the CTA queue, copy their chunks into the ring ---------
     constexpr int PPR = GE::CB / 16;                 // 16-byte pieces per row of a full chunk
     constexpr int RPI = 32 / PPR;                    // rows covered by one warp-wide copy instruction
     const int lrow = lane / PPR, lcol = lane % PPR;
-    auto issue = [&](bool valid, int tile, int ch, int s) {
-        if (valid) {
-            const int pieces = min(GE::CB, p.row_bytes - ch * GE::CB) >> 4;
-            if (lcol < pieces) {
-                const uint32_t dst = ring_u32 + s * GE::STAGE_BYTES + lcol * 16;
-                const uint8_t* src = a.packed + (size_t)ch * GE::CB + lcol * 16;
+    // Runs are dealt round-robin: warp w takes runs r0 + w, r0 + w + nw, ...
+    int pf_run = r0 + warp, pf_tile = 0, pf_j = 0, pf_ch = 0, pf_end = 0;     // pf_j: run index inside the tile
+    if (pf_run < r1) {
+        pf_tile = pf_run / p.rpt;
+        pf_j = pf_run - pf_tile * p.rpt;
+        pf_ch = pf_j * p.rlen;
+        pf_end = min(pf_ch + p.rlen, p.nch);
+    } else {
+        pf_run = -1;
+    }
+    // Per-lane constants of the copy pattern: one instruction moves RPI rows x 128 bytes.
+    constexpr int NIT = kTileRows / RPI;
+    const size_t tile_stride = (size_t)kTileRows * a.ldp;
+    const size_t it_stride = (size_t)RPI * a.ldp;
+    const uint8_t* lane_src = a.packed + (size_t)lrow * a.ldp + lcol * 16;
+    uint32_t dst_off[NIT];
 #pragma unroll
-                for (int it = 0; it < kTileRows / RPI; ++it) {
-                    const int r = it * RPI + lrow;
-                    const int row = min(tile * kTileRows + r, a.n - 1);
-                    cp_async16(dst + r * GE::PITCH, src + (size_t)row * a.ldp);
+    for (int it = 0; it < NIT; ++it) {
+        const int r = it * RPI + lrow;
+        dst_off[it] = r * GE::PITCH + ((lcol ^ GE::swz(r)) << 4);
+    }
+    const __half* lane_sc = a.scales + (size_t)min(lane, kTileRows - 1) * a.lds;
+    const size_t sc_tile_stride = (size_t)kTileRows * a.lds;
+    const bool ragged_n = (a.n % kTileRows) != 0;
+    auto issue_next = [&](int s) {
+        if (pf_run >= 0 && pf_ch == pf_end) {          // current run exhausted: step to this warp's next run
+            pf_run += p.nw;
+            pf_j += p.nw;
+            while (pf_j >= p.rpt) { pf_j -= p.rpt; ++pf_tile; }
+            if (pf_run < r1) {
+                pf_ch = pf_j * p.rlen;
+                pf_end = min(pf_ch + p.rlen, p.nch);
+            } else {
+                pf_run = -1;
+            }
+        }
+        if (pf_run >= 0) {
+            const int ngr = min(GE::CG, p.ng - pf_ch * GE::CG);
+            const int pieces = (ngr * GB) >> 4;
+            const uint32_t sbase = ring_u32 + s * GE::STAGE_BYTES;
+            const bool edge = ragged_n && pf_tile == p.nt - 1;        // rows past N are clamped to the last row
+            if (lcol < pieces) {
+                if (!edge) {
+                    const uint8_t* src = lane_src + (size_t)pf_tile * tile_stride + (size_t)pf_ch * GE::CB;
+#pragma unroll
+                    for (int it = 0; it < NIT; ++it) cp_async16(sbase + dst_off[it], src + it * it_stride);
+                } else {
+                    const uint8_t* src = a.packed + (size_t)pf_ch * GE::CB + lcol * 16;
+#pragma unroll
+                    for (int it = 0; it < NIT; ++it) {
+                        const int row = min(pf_tile * kTileRows + it * RPI + lrow, a.n - 1);
+                        cp_async16(sbase + dst_off[it], src + (size_t)row * a.ldp);
+                    }
                 }
             }
+            if (lane < kTileRows) {                   // this row's scales for the chunk
+                const __half* src = edge ? a.scales + (size_t)min(pf_tile * kTileRows + lane, a.n - 1) * a.lds + pf_ch * GE::CG
+                                         : lane_sc + (size_t)pf_tile * sc_tile_stride + pf_ch * GE::CG;
+                const uint32_t dst = sbase + GE::SCALE_OFF + lane * 16;
+                if (p.scales_async && ngr == GE::CG) {
+                    if constexpr (GE::CG == 8) cp_async16(dst, src);
+                    else if constexpr (GE::CG == 4) cp_async8(dst, src);
+                    else cp_async4(dst, src);
+                } else {
+                    __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16);
+                    for (int i = 0; i < ngr; ++i) d[i] = __ldg(src + i);
+                }
+            }
+            if (lane == 0) meta[s] = make_int4(pf_tile, pf_ch, pf_run - r0, pf_ch + 1 == pf_end);
+            ++pf_ch;
+        } else if (lane == 0) {
+            meta[s] = make_int4(-1, 0, 0, 0);
         }
         cp_async_commit();
     };
 
-    // prefetch cursor (pf_*) runs `stages` units ahead of the consume cursor
-    int pf = u0, pf_tile = u0 / p.nch, pf_ch = u0 - pf_tile * p.nch;
-    auto advance_pf = [&]() { ++pf; if (++pf_ch == p.nch) { pf_ch = 0; ++pf_tile; } };
     stage_activations<BITS, GB, M, BF16>(p, smem, [&]() {
-        for (int s = 0; s < p.stages; ++s) { issue(pf < u1, pf_tile, pf_ch, s); advance_pf(); }
-        QTRACE(1);
-    });                                                   // CTA-wide, ends with __syncthreads()
+        // (runs after the barrier that follows the activation loads; the queue head is visible)
+        QTRACE(7);
+        // Oldest group: the epilogue operands of the tile this warp will finish first.
+        const int etile = T0 + warp;
+        const bool efull = etile <= T1 && etile * p.rpt >= r0 && (etile + 1) * p.rpt <= r1 &&
+                           (etile + 1) * kTileRows <= a.n;
+        if (p.epi_async && efull) {
+            const int opieces = p.ocb >> 4, upieces = p.rb >> 4;
+            for (int i = lane; i < kTileRows * opieces; i += 32) {
+                const int r = i / opieces, c = i - r * opieces;
+                cp_async16(smem_u32(epi) + r * p.ocb + c * 16,
+                           reinterpret_cast<const unsigned char*>(a.ow + (size_t)(etile * kTileRows + r) * a.ldow) + c * 16);
+            }
+            for (int i = lane; i < kTileRows * upieces; i += 32) {
+                const int r = i / upieces, c = i - r * upieces;
+                cp_async16(smem_u32(epi) + kTileRows * p.ocb + r * p.rb + c * 16,
+                           reinterpret_cast<const unsigned char*>(a.ru + (size_t)(etile * kTileRows + r) * a.ldu) + c * 16);
+            }
+            if (a.bias && lane < 2)
+                cp_async16(smem_u32(epi) + kTileRows * (p.ocb + p.rb) + lane * 16,
+                           reinterpret_cast<const unsigned char*>(a.bias + (size_t)etile * kTileRows) + lane * 16);
+        }
+        cp_async_commit();
+        issue_next(0);                                // the rest of the ring is filled while computing: a warp that
+        QTRACE(1);                                    // queued it all here would sit behind its own copies
+    });
+    issue_next(1);
+    __syncthreads();                                  // staged activations visible to every warp
     QTRACE(2);
 
-    const float2* gx = reinterpret_cast<const float2*>(smem + p.off_sumx);
+    const float2* gx = reinterpret_cast<const float2*>(smem + p.off_gx);
     const uint4* xs16 = reinterpret_cast<const uint4*>(smem + p.off_xs);
+    const uint4* xs_lane = xs16 + g * 4 + t;
     const int ma = min(2 * t, M - 1), mb = min(2 * t + 1, M - 1);
+    unsigned char* slots = smem + p.off_slots;
 
-    // scales of a unit (raw fp16), one per (row g / g+8, group of the chunk), fetched one unit ahead
-    __half sc0[GE::CG], sc1[GE::CG];
-    auto load_scales = [&](int tile, int ch, __half (&d0)[GE::CG], __half (&d1)[GE::CG]) {
-        const int ra = min(tile * kTileRows + g, a.n - 1), rb = min(tile * kTileRows + g + 8, a.n - 1);
-        const __half* pa = a.scales + (size_t)ra * a.lds + ch * GE::CG;
-        const __half* pb = a.scales + (size_t)rb * a.lds + ch * GE::CG;
-        const int ngr = min(GE::CG, p.ng - ch * GE::CG);
-#pragma unroll
-        for (int i = 0; i < GE::CG; ++i) {
-            d0[i] = i < ngr ? __ldg(pa + i) : __half(0.0f);
-            d1[i] = i < ngr ? __ldg(pb + i) : __half(0.0f);
-        }
-    };
-    int tile = u0 / p.nch, ch = u0 - tile * p.nch;
-    const int my_first_tile = tile;
-    if (u0 < u1) load_scales(tile, ch, sc0, sc1);
-
+    // ---- consumer side ------------------------------------------------------------------------
     float y[4] = {0.f, 0.f, 0.f, 0.f};
-    int seg_first_ch = ch;
-    int stage = 0;
-
-    for (int u = u0; u < u1; ++u) {
-        int ntile = tile, nch_ = ch + 1;
-        if (nch_ == p.nch) { nch_ = 0; ++ntile; }
-        __half nsc0[GE::CG], nsc1[GE::CG];
-        if (u + 1 < u1) load_scales(ntile, nch_, nsc0, nsc1);
-
-        cp_async_wait_dyn(p.stages - 1);        // all but the newest stages-1 groups are done: unit u has landed
+    int stage = 0;                              // slot being consumed
+    int fill = p.stages > 2 ? 2 : 0;            // next slot to fill (two copies are already queued)
+    int ahead = 2;                              // copies queued and not yet consumed
+    bool first = true;
+    for (;;) {
+        // Top the ring up, at most two copies per iteration, so that the ramp-up is spread over
+        // the first iterations instead of blocking every warp before it computes anything.
+        for (int k = 0; k < 2 && ahead < p.stages; ++k) {
+            issue_next(fill);
+            fill = fill + 1 == p.stages ? 0 : fill + 1;
+            ++ahead;
+        }
+        cp_async_wait_dyn(ahead - 1);           // everything but the newest ahead-1 groups is done: this slot has landed
         __syncwarp();
-        if (u == u0) QTRACE(3);
+        const int4 mt = meta[stage];
+        if (mt.x < 0) break;
+        if (first) { QTRACE(3); first = false; }
+        const int ch = mt.y;
         const int ngr = min(GE::CG, p.ng - ch * GE::CG);
-        const unsigned char* base0 = ring + stage * GE::STAGE_BYTES + g * GE::PITCH + t * GE::TB;
-        const unsigned char* base1 = base0 + 8 * GE::PITCH;
+        const unsigned char* sb = ring + stage * GE::STAGE_BYTES;
+        const unsigned char* row0 = sb + g * GE::PITCH;            // rows g and g+8 share the swizzle
+        const unsigned char* row1 = row0 + 8 * GE::PITCH;
+        const int sw = GE::swz(g);
+        __align__(16) __half sc0[8], sc1[8];
+        if constexpr (GE::CG == 8) {
+            *reinterpret_cast<uint4*>(sc0) = *reinterpret_cast<const uint4*>(sb + GE::SCALE_OFF + g * 16);
+            *reinterpret_cast<uint4*>(sc1) = *reinterpret_cast<const uint4*>(sb + GE::SCALE_OFF + (g + 8) * 16);
+        } else if constexpr (GE::CG == 4) {
+            *reinterpret_cast<uint2*>(sc0) = *reinterpret_cast<const uint2*>(sb + GE::SCALE_OFF + g * 16);
+            *reinterpret_cast<uint2*>(sc1) = *reinterpret_cast<const uint2*>(sb + GE::SCALE_OFF + (g + 8) * 16);
+        } else {
+            *reinterpret_cast<uint32_t*>(sc0) = *reinterpret_cast<const uint32_t*>(sb + GE::SCALE_OFF + g * 16);
+            *reinterpret_cast<uint32_t*>(sc1) = *reinterpret_cast<const uint32_t*>(sb + GE::SCALE_OFF + (g + 8) * 16);
+        }
 #pragma unroll
         for (int gi = 0; gi < GE::CG; ++gi) {
             if (gi < ngr) {
                 const int G = ch * GE::CG + gi;
                 uint32_t w0[GE::TW], w1[GE::TW];
+                // logical byte offset of this lane's TB bytes -> swizzled 16-byte piece + offset in it
+                const int lo = gi * GB + t * GE::TB;
+                const int off = (((lo >> 4) ^ sw) << 4) + (lo & 15);
                 if constexpr (GE::TW == 1) {
-                    w0[0] = *reinterpret_cast<const uint32_t*>(base0 + gi * GB);
-                    w1[0] = *reinterpret_cast<const uint32_t*>(base1 + gi * GB);
+                    w0[0] = *reinterpret_cast<const uint32_t*>(row0 + off);
+                    w1[0] = *reinterpret_cast<const uint32_t*>(row1 + off);
                 } else if constexpr (GE::TW == 2) {
-                    const uint2 v0 = *reinterpret_cast<const uint2*>(base0 + gi * GB);
-                    const uint2 v1 = *reinterpret_cast<const uint2*>(base1 + gi * GB);
+                    const uint2 v0 = *reinterpret_cast<const uint2*>(row0 + off);
+                    const uint2 v1 = *reinterpret_cast<const uint2*>(row1 + off);
                     w0[0] = v0.x; w0[1] = v0.y; w1[0] = v1.x; w1[1] = v1.y;
                 } else {
-                    const uint4 v0 = *reinterpret_cast<const uint4*>(base0 + gi * GB);
-                    const uint4 v1 = *reinterpret_cast<const uint4*>(base1 + gi * GB);
+                    const uint4 v0 = *reinterpret_cast<const uint4*>(row0 + off);
+                    const uint4 v1 = *reinterpret_cast<const uint4*>(row1 + off);
                     w0[0] = v0.x; w0[1] = v0.y; w0[2] = v0.z; w0[3] = v0.w;
                     w1[0] = v1.x; w1[1] = v1.y; w1[2] = v1.z; w1[3] = v1.w;
                 }
                 // two independent accumulator chains (the classes alternate between them)
                 float accA[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint4* xg = xs16 + ((size_t)(G * GE::TW) * (GE::NCLS / 2) * M + g) * 4 + t;
+                const uint4* xg = xs_lane + G * (GE::TW * (GE::NCLS / 2) * M * 4);
 #pragma unroll
                 for (int i = 0; i < GE::TW; ++i) {
                     const uint32_t h0 = w0[i] >> 8, h1 = w1[i] >> 8;
 #pragma unroll
                     for (int cp = 0; cp < GE::NCLS / 2; ++cp) {
                         uint4 b = make_uint4(0u, 0u, 0u, 0u);
-                        if (g < M) b = xg[(size_t)(i * (GE::NCLS / 2) + cp) * M * 4];
+                        if (g < M) b = xg[(i * (GE::NCLS / 2) + cp) * M * 4];
                         constexpr uint32_t MK = GE::MASK;
                         const uint32_t m0 = MK << (BITS * (2 * cp)), m1 = MK << (BITS * (2 * cp + 1));
                         mma_f16(accA, w0[i] & m0, w1[i] & m0, h0 & m0, h1 & m0, b.x, b.y);
@@ -466,68 +611,87 @@ __global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant
                     }
                 }
                 const float s0 = __half2float(sc0[gi]), s1 = __half2float(sc1[gi]);
-                const float2 ga = gx[G * M + ma], gb = gx[G * M + mb];
+                float2 ga, gb;
+                if constexpr (M % 2 == 0) {           // the two columns of this lane are neighbours: one 16-byte read
+                    const float4 gq = *reinterpret_cast<const float4*>(gx + G * M + (M >= 2 ? min(2 * t, M - 2) : 0));
+                    ga = make_float2(gq.x, gq.y); gb = make_float2(gq.z, gq.w);
+                } else {
+                    ga = gx[G * M + ma]; gb = gx[G * M + mb];
+                }
                 y[0] = fmaf(s0, fmaf(ga.y, accA[0] + accB[0], -ga.x), y[0]);
                 y[1] = fmaf(s0, fmaf(gb.y, accA[1] + accB[1], -gb.x), y[1]);
                 y[2] = fmaf(s1, fmaf(ga.y, accA[2] + accB[2], -ga.x), y[2]);
                 y[3] = fmaf(s1, fmaf(gb.y, accA[3] + accB[3], -gb.x), y[3]);
             }
         }
-        __syncwarp();
-        issue(pf < u1, pf_tile, pf_ch, stage);
-        advance_pf();
-        stage = stage + 1 == p.stages ? 0 : stage + 1;
-#pragma unroll
-        for (int i = 0; i < GE::CG; ++i) { sc0[i] = nsc0[i]; sc1[i] = nsc1[i]; }
-
-        if (u == u1 - 1) QTRACE(4);
-        if (ch == p.nch - 1 || u == u1 - 1) {
-            if (seg_first_ch == 0 && ch == p.nch - 1) {
-                finish_tile<M, BF16>(p, smem, tile, y);
-            } else {
-                // Partial tile: park the partial sums, count arrivals, last one in adds them up in warp order.
-                const int slot = tile == my_first_tile ? 0 : 1;
-                float* mine = a.partial + ((size_t)(gw * 2 + slot) * 4) * 32;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) mine[i * 32 + lane] = y[i];
-                __threadfence();
-                __syncwarp();
-                const int wf = owner_of(tile * p.nch, U, W);
-                const int wl = owner_of(tile * p.nch + p.nch - 1, U, W);
-                int last = 0;
-                if (lane == 0) {
-                    const int old = atomicAdd(&a.counters[tile], 1);
-                    last = old == wl - wf;
-                    if (last) a.counters[tile] = 0;          // ready for the next launch
-                }
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-                    y[0] = y[1] = y[2] = y[3] = 0.f;
-                    for (int wb = wf; wb <= wl; wb += 4) {     // four contributors' loads in flight at a time
-                        float v[4][4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int w = min(wb + k, wl);
-                            const int s = tile == first_unit(w, U, W) / p.nch ? 0 : 1;
-                            const float* src = a.partial + ((size_t)(w * 2 + s) * 4) * 32;
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) v[k][i] = ld_cg_f32(src + i * 32 + lane);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (wb + k <= wl) {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) y[i] += v[k][i];
-                            }
-                    }
-                    finish_tile<M, BF16>(p, smem, tile, y);
-                }
-            }
+        if (mt.w) {                                   // run complete: park its partial sums
+            if (t < TT) *reinterpret_cast<float4*>(slots + (size_t)mt.z * SLOT_BYTES + (g * TT + t) * 16) =
+                            make_float4(y[0], y[1], y[2], y[3]);
             y[0] = y[1] = y[2] = y[3] = 0.f;
-            seg_first_ch = 0;
         }
-        tile = ntile; ch = nch_;
+        __syncwarp();                               // every lane is done reading the slot before it is refilled
+        --ahead;
+        stage = stage + 1 == p.stages ? 0 : stage + 1;
+    }
+    cp_async_wait<0>();
+    QTRACE(4);
+    __syncthreads();                                  // every run of this CTA is parked
+
+    // ---- tiles: add the runs in order, finish or hand over --------------------------------------
+    for (int tile = T0 + warp; tile <= T1; tile += p.nw) {
+        const int lo = max(r0, tile * p.rpt), hi = min(r1, (tile + 1) * p.rpt);
+        y[0] = y[1] = y[2] = y[3] = 0.f;
+        if (t < TT) {
+            for (int r = lo; r < hi; ++r) {
+                const float4 v = *reinterpret_cast<const float4*>(slots + (size_t)(r - r0) * SLOT_BYTES + (g * TT + t) * 16);
+                y[0] += v.x; y[1] += v.y; y[2] += v.z; y[3] += v.w;
+            }
+        }
+        const bool whole = lo == tile * p.rpt && hi == (tile + 1) * p.rpt;
+        if (whole) {
+            const bool pre = p.epi_async && tile == T0 + warp && (tile + 1) * kTileRows <= a.n;
+            finish_tile<M, BF16>(p, smem, tile, y, pre ? epi : nullptr);
+        } else {
+            // Tile shared with neighbouring CTAs: park this CTA's sum in global memory, count
+            // arrivals, and let the last CTA to arrive add the contributions in CTA order.
+            const int slot = tile == T0 ? 0 : 1;
+            float* mine = a.partial + ((size_t)(cta * 2 + slot) * 4) * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mine[i * 32 + lane] = y[i];
+            __threadfence();
+            __syncwarp();
+            const int cf = owner_of(tile * p.rpt, p.runs, grid);
+            const int cl = owner_of(tile * p.rpt + p.rpt - 1, p.runs, grid);
+            int last = 0;
+            if (lane == 0) {
+                const int old = atomicAdd(&a.counters[tile], 1);
+                last = old == cl - cf;
+                if (last) a.counters[tile] = 0;          // ready for the next launch
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence();
+                y[0] = y[1] = y[2] = y[3] = 0.f;
+                for (int cb = cf; cb <= cl; cb += 4) {     // four contributors' loads in flight at a time
+                    float v[4][4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int c = min(cb + k, cl);
+                        const int sl = tile == first_unit(c, p.runs, grid) / p.rpt ? 0 : 1;
+                        const float* src = a.partial + ((size_t)(c * 2 + sl) * 4) * 32;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[k][i] = ld_cg_f32(src + i * 32 + lane);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (cb + k <= cl) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) y[i] += v[k][i];
+                        }
+                }
+                finish_tile<M, BF16>(p, smem, tile, y, nullptr);
+            }
+        }
     }
     QTRACE(5);
 }
@@ -560,7 +724,21 @@ int launch_one(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
             return check_launch("cudaFuncSetAttribute(qgemv_mma_kernel)");
         configured[dev] = true;
     }
-    kern<<<grid, p.nw * 32, smem_bytes, s>>>(p);
+    // Programmatic dependent launch: the grid may become resident while the previous kernel in the
+    // stream is still running.  When that kernel is this call's own residual-projection kernel
+    // (launched in full stream order), x is already final and only the epilogue waits for it;
+    // otherwise the kernel waits for its predecessors before it touches x (p.wait_for_x).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(p.nw * 32);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) return check_launch("qgemv_mma_kernel");
     return check_launch("qgemv_mma_kernel");
 }
 
@@ -595,36 +773,69 @@ MmaPlan plan_mma(const qgemv_problem& p) {
     auto al = [](const void* q, size_t a) { return reinterpret_cast<uintptr_t>(q) % a == 0; };
     if (!al(p.packed, 16) || p.ldp % 16 || !al(p.x, 16) || p.ldx % 8) return pl;
     if (p.outliers > kMaxOutliers || p.rank > kMaxRank) return pl;
-    const int cg = (256 / gb) > 8 ? 8 : (256 / gb);
-    const int cb = cg * gb, pitch = cb + gb, stage_bytes = kTileRows * pitch;
+    const int cb = 128, cg = cb / gb, stage_bytes = kTileRows * cb + kTileRows * 16;
     pl.gb = gb;
     pl.ng = p.k_padded / p.group;
     pl.nch = (pl.ng + cg - 1) / cg;
     pl.nt = (p.n + kTileRows - 1) / kTileRows;
     if (pl.nt > kWsMaxCounters - 1) return pl;
-    int off = 1024;
-    pl.off_xo = off;   off = align_up(off + p.outliers * p.m * 4, 16);
-    pl.off_tt = off;   off = align_up(off + p.rank * p.m * 4, 16);
-    pl.off_sumx = off; off = align_up(off + pl.ng * p.m * 8, 16);
-    pl.off_xs = off;   off = align_up(off + p.m * p.k_padded * 2, 128);
-    pl.off_ring = off;
-    // Most warps first (latency hiding), at least 3 ring slots each if possible.
-    int nw = 0, stages = 0;
+    if ((long long)pl.nt * pl.nch > 0x3fffffff) return pl;
+    const int sms = sm_count();
+    // Runs: consecutive chunks of one tile.  One chunk per run unless a CTA would then need more
+    // than 32 KB of shared memory for the partial sums of its runs.
+    const int slot_bytes = 8 * ((p.m + 1) / 2) * 16;
+    int rlen = 1, rpt = pl.nch, grid = 0, slot_cap = 0;
+    for (;; rlen *= 2) {
+        rpt = (pl.nch + rlen - 1) / rlen;
+        const long long runs = (long long)pl.nt * rpt;
+        grid = (int)(runs < sms ? runs : sms);
+        slot_cap = (int)((runs + grid - 1) / grid) + 1;
+        if (slot_cap * slot_bytes <= 32768 || rlen >= pl.nch) break;
+    }
+    if (slot_cap * slot_bytes > 65536) return pl;
+    pl.rlen = rlen; pl.rpt = rpt; pl.grid = grid;
+    // whole tiles per CTA if the busiest CTA then has at most 20 % more than the average
+    pl.tile_aligned = 0;
+    if (pl.nt >= grid) {
+        const int most = (pl.nt + grid - 1) / grid;
+        if ((long long)most * grid * 5 <= (long long)pl.nt * 6) pl.tile_aligned = 1;
+    }
+    if (pl.tile_aligned) slot_cap = ((pl.nt + grid - 1) / grid) * rpt;
+    if (slot_cap * slot_bytes > 65536) return pl;
+    if ((size_t)grid * 2 * 4 * 32 > kMaxPartialFloats) return pl;
+    pl.scales_async = (p.lds % cg == 0) && al(p.scales, (size_t)cg * 2) ? 1 : 0;
+    pl.ocb = align_up(p.outliers * 2, 16);
+    pl.rb = align_up(p.rank * 2, 16);
+    bool epi = (p.outliers > 0 || p.rank > 0 || p.bias != nullptr);
+    if (p.outliers > 0 && (p.outliers % 8 || p.ldow % 8 || !al(p.outlier_w, 16))) epi = false;
+    if (p.rank > 0 && (p.rank % 8 || p.ldu % 8 || !al(p.res_u, 16))) epi = false;
+    if (p.bias && !al(p.bias, 16)) epi = false;
+    pl.epi_async = epi ? 1 : 0;
+
+    int off = 64;
+    pl.off_xo = off;    off = align_up(off + p.outliers * p.m * 4, 16);
+    pl.off_gx = off;    off = align_up(off + pl.ng * p.m * 8, 16);
+    pl.off_slots = off; off = align_up(off + slot_cap * slot_bytes, 128);
+    pl.off_xs = off;    off = align_up(off + p.m * p.k_padded * 2, 128);
+    // per warp: 4 ring descriptors (64 B) + the epilogue prefetch buffer + the ring itself
+    const int epi_bytes = align_up(kTileRows * (pl.ocb + pl.rb) + 32, 16);
     const int avail = kMaxDynSmem - off;
+    int nw = 0, stages = 0;
     for (int want = 3; want >= 2 && !nw; --want)
-        for (int cand = 16; cand >= 4; cand -= 4)
-            if (avail / (cand * stage_bytes) >= want) { nw = cand; stages = avail / (cand * stage_bytes); break; }
+        for (int cand = 16; cand >= 4; cand -= 4) {
+            const int fixed = cand * (64 + epi_bytes);
+            if (avail > fixed && (avail - fixed) / (cand * stage_bytes) >= want) {
+                nw = cand; stages = (avail - fixed) / (cand * stage_bytes); break;
+            }
+        }
     if (!nw) return pl;
     if (stages > 4) stages = 4;
-    if ((long long)pl.nt * pl.nch > 0x3fffffff) return pl;
-    pl.nw = nw;
-    pl.stages = stages;
-    pl.off_bar = 0;
+    pl.nw = nw; pl.stages = stages;
+    pl.off_meta = off;  off += nw * 64;
+    pl.off_epi = off;   off = align_up(off + nw * epi_bytes, 128);
+    pl.epi_bytes = epi_bytes;
+    pl.off_ring = off;
     pl.smem_bytes = off + nw * stages * stage_bytes;
-    const long long units = (long long)pl.nt * pl.nch;
-    const int sms = sm_count();
-    pl.grid = (int)(units < sms ? units : sms);
-    if ((size_t)pl.grid * nw * 2 * 4 * 32 > kMaxPartialFloats) return pl;
     static const char* names[2][3] = {{"mma_int2_g64", "mma_int2_g128", "mma_int2_g256"},
                                       {"mma_int4_g32", "mma_int4_g64", "mma_int4_g128"}};
     pl.name = names[p.bits == 2 ? 0 : 1][gb == 16 ? 0 : gb == 32 ? 1 : 2];
@@ -638,10 +849,13 @@ int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, cudaStream
     p.nt = pl.nt; p.nch = pl.nch; p.ng = pl.ng;
     p.row_bytes = a.kpad * bits / 8;
     p.nw = pl.nw; p.stages = pl.stages;
-    p.units = pl.nt * pl.nch;
-    p.total_warps = p.units < pl.grid * pl.nw ? p.units : pl.grid * pl.nw;
-    p.off_xo = pl.off_xo; p.off_tt = pl.off_tt; p.off_sumx = pl.off_sumx; p.off_xs = pl.off_xs;
-    p.off_ring = pl.off_ring;
+    p.rlen = pl.rlen; p.rpt = pl.rpt; p.runs = pl.nt * pl.rpt;
+    p.scales_async = pl.scales_async; p.epi_async = pl.epi_async; p.ocb = pl.ocb; p.rb = pl.rb;
+    p.epi_bytes = pl.epi_bytes;
+    p.off_xo = pl.off_xo; p.off_gx = pl.off_gx; p.off_slots = pl.off_slots; p.off_epi = pl.off_epi;
+    p.off_meta = pl.off_meta; p.off_xs = pl.off_xs; p.off_ring = pl.off_ring;
+    p.wait_for_x = a.rank > 0 ? 0 : 1;
+    p.tile_aligned = pl.tile_aligned;
     return bits == 2 ? launch_gb<2>(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s)
                      : launch_gb<4>(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s);
 }

@@ -220,25 +220,47 @@ __global__ void __launch_bounds__(kThreads) qgemv_simt_kernel(const Args a) {
     }
 }
 
-// t[m][r] = sum_{k < Korig} res_v[r, k] * x[m, k]   (fp32), one block per (r, m).
+// t[m][r] = sum_{k < Korig} res_v[r, k] * x[m, k]   (fp32).  One block per residual row r.
+// Launched in full stream order (so x is final once any block of it runs); the fused kernel
+// that follows carries the programmatic-serialisation attribute, may start as soon as every
+// block here has executed griddepcontrol.launch_dependents, reads x at once and reads t only
+// after its own griddepcontrol.wait.
 template <bool BF16>
 __global__ void __launch_bounds__(256) residual_t_kernel(const Args a) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     using XT = typename Act16<BF16>::T;
-    const int r = blockIdx.x, m = blockIdx.y;
-    const XT* x = static_cast<const XT*>(a.x) + (size_t)m * a.ldx;
+    const int r = blockIdx.x;
+    const XT* x = static_cast<const XT*>(a.x);
     const __half* v = a.rv + (size_t)r * a.ldv;
-    float s = 0.0f;
-    for (int k = threadIdx.x; k < a.korig; k += blockDim.x)
-        s = fmaf(__half2float(v[k]), Act16<BF16>::to_float(x[k]), s);
-    __shared__ float red[8];
+    float s[QGEMV_MAX_M] = {0.f, 0.f, 0.f, 0.f};
+    const bool vec = (reinterpret_cast<uintptr_t>(v) % 16 == 0) && (a.ldv % 8 == 0) &&
+                     (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (a.ldx % 8 == 0);
+    const int k8 = vec ? a.korig / 8 : 0;
+    for (int i = threadIdx.x; i < k8; i += blockDim.x) {
+        const uint4 vv = reinterpret_cast<const uint4*>(v)[i];
+        const __half* vh = reinterpret_cast<const __half*>(&vv);
+        for (int m = 0; m < a.m; ++m) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + (size_t)i * 8);
+            const XT* xh = reinterpret_cast<const XT*>(&xv);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+            for (int q = 0; q < 8; ++q) s[m] = fmaf(__half2float(vh[q]), Act16<BF16>::to_float(xh[q]), s[m]);
+        }
+    }
+    for (int k = k8 * 8 + threadIdx.x; k < a.korig; k += blockDim.x)
+        for (int m = 0; m < a.m; ++m)
+            s[m] = fmaf(__half2float(v[k]), Act16<BF16>::to_float(x[(size_t)m * a.ldx + k]), s[m]);
+    __shared__ float red[8][QGEMV_MAX_M];
+#pragma unroll
+    for (int m = 0; m < QGEMV_MAX_M; ++m) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s[m] += __shfl_xor_sync(0xffffffffu, s[m], o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5][m] = s[m];
+    }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < a.m) {
         float tot = 0.0f;
-        for (int i = 0; i < 8; ++i) tot += red[i];
-        a.t[m * kMaxRank + r] = tot;
+        for (int i = 0; i < 8; ++i) tot += red[i][threadIdx.x];
+        a.t[threadIdx.x * kMaxRank + r] = tot;
     }
 }
 
@@ -270,7 +292,7 @@ int launch_simt_b(const Args& a, bool bf16, int unit, cudaStream_t s) {
 }  // namespace
 
 int launch_residual_t(const Args& a, bool bf16, cudaStream_t s) {
-    dim3 grid(a.rank, a.m), block(256);
+    dim3 grid(a.rank), block(256);
     if (bf16) residual_t_kernel<true><<<grid, block, 0, s>>>(a);
     else      residual_t_kernel<false><<<grid, block, 0, s>>>(a);
     return check_launch("residual_t_kernel");

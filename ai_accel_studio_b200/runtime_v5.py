@@ -1,0 +1,190 @@
+"""StaticCache decode runtime for models whose Linear layers were swapped for the packed modules.
+
+Mirrors ``ai_accel_lab/runtime_v5.py`` of the reference project: ``prepare_static_compile``
+(:7-23) and ``generate_static_benchmark`` (:29-73, same timing protocol: warm-ups, one timed
+prefill = TTFT, one timed fixed-length greedy generation, decode tok/s = generated /
+(total - TTFT)).  Two things differ:
+
+* Token ids can be passed directly (``input_ids=``): the benchmark configurations use random
+  prompts, and no tokenizer files are needed for them.
+* ``StaticGraphDecoder`` is the native decode path: the one-token forward over a
+  ``StaticCache`` is captured once into an explicit CUDA graph and replayed per token, instead of
+  going through ``torch.compile(mode='reduce-overhead')``.  ``prepare_static_compile`` is kept
+  for callers that want the reference's compiled path; the packed ops are registered custom ops
+  with fake kernels, so Dynamo traces through them.
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+
+
+def prepare_static_compile(model, fullgraph=False):
+    """Static KV cache + ``torch.compile(mode='reduce-overhead')`` on ``model.forward``.
+    Returns ``(model, status)`` like the reference."""
+    status = {"static_cache": False, "compiled": False, "graph_safe_custom_layers": 0, "error": None}
+    try:
+        for mod in model.modules():
+            if hasattr(mod, "graph_safe"):
+                mod.graph_safe = True
+                status["graph_safe_custom_layers"] += 1
+        if hasattr(model, "generation_config"):
+            model.generation_config.cache_implementation = "static"
+            status["static_cache"] = True
+        model.forward = torch.compile(model.forward, mode="reduce-overhead", fullgraph=fullgraph)
+        status["compiled"] = True
+    except Exception as e:  # same soft-fail contract as the reference
+        status["error"] = repr(e)
+    return model, status
+
+
+def _cuda_event_ms(fn):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    r = fn()
+    end.record()
+    end.synchronize()
+    return r, float(start.elapsed_time(end))
+
+
+class StaticGraphDecoder:
+    """Greedy decoding with a StaticCache and one captured CUDA graph for the decode step.
+
+    ``prefill(input_ids)`` runs the prompt eagerly and returns the first generated token;
+    ``decode(n)`` replays the captured single-token step ``n`` times with no host
+    synchronisation in between and returns the ``[B, n]`` tokens.
+    """
+
+    def __init__(self, model, batch_size: int, max_cache_len: int, device=None, dtype=None):
+        from transformers import StaticCache
+        self.model = model
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        self.batch = int(batch_size)
+        self.max_len = int(max_cache_len)
+        for mod in model.modules():
+            if hasattr(mod, "graph_safe"):
+                mod.graph_safe = True
+        self.cache = StaticCache(config=model.config, max_cache_len=self.max_len)
+        self.tok = torch.zeros((self.batch, 1), dtype=torch.long, device=self.device)
+        self.pos = torch.zeros((1,), dtype=torch.long, device=self.device)
+        self.graph = None
+        self.out_tok = None
+
+    @torch.no_grad()
+    def _step(self):
+        out = self.model(input_ids=self.tok, past_key_values=self.cache, cache_position=self.pos, use_cache=True)
+        nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+        self.tok.copy_(nxt)
+        self.pos.add_(1)
+        return nxt
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        b, n = input_ids.shape
+        if b != self.batch or n >= self.max_len:
+            raise ValueError("prompt does not fit the decoder's batch size / cache length")
+        self.cache.reset()
+        out = self.model(input_ids=input_ids, past_key_values=self.cache,
+                         cache_position=torch.arange(n, device=self.device), use_cache=True)
+        nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+        self.tok.copy_(nxt)
+        self.pos.fill_(n)
+        return nxt
+
+    @torch.no_grad()
+    def capture(self):
+        """Capture the decode step (call after a prefill; the cache contents are left intact
+        apart from the warm-up positions, which the next prefill overwrites)."""
+        if self.device.type != "cuda":
+            raise RuntimeError("CUDA graphs need a CUDA device")
+        saved_tok, saved_pos = self.tok.clone(), self.pos.clone()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._step()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self.tok.copy_(saved_tok)
+        self.pos.copy_(saved_pos)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out_tok = self._step()
+        self.tok.copy_(saved_tok)
+        self.pos.copy_(saved_pos)
+
+    @torch.no_grad()
+    def decode(self, n_tokens: int) -> torch.Tensor:
+        if int(self.pos.item()) + n_tokens > self.max_len:
+            raise ValueError("cache too short for the requested number of tokens")
+        toks = torch.empty((self.batch, n_tokens), dtype=torch.long, device=self.device)
+        for i in range(n_tokens):
+            if self.graph is not None:
+                self.graph.replay()
+                toks[:, i:i + 1] = self.out_tok
+            else:
+                toks[:, i:i + 1] = self._step()
+        return toks
+
+
+@torch.no_grad()
+def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens=64, device="cuda", warmups=2,
+                              input_ids=None, use_cuda_graph=True):
+    """Fixed-length greedy generation benchmark (reference protocol, ai_accel_lab/runtime_v5.py:29-73).
+
+    Either ``tokenizer`` + ``prompt`` (left-padded to a multiple of 8, as the reference does) or
+    ``input_ids`` directly.  Returns a dict with the reference's keys (``ttft_ms``,
+    ``decode_tokens_s``, ``total_tokens_s``, ``generated_tokens``, ``prompt_tokens``, memory
+    figures) plus ``tokens`` (the generated ids)."""
+    if input_ids is None:
+        if tokenizer is None or prompt is None:
+            raise ValueError("pass input_ids, or tokenizer and prompt")
+        old = getattr(tokenizer, "padding_side", "right")
+        tokenizer.padding_side = "left"
+        if getattr(tokenizer, "pad_token_id", None) is None and getattr(tokenizer, "eos_token_id", None) is not None:
+            tokenizer.pad_token_id = tokenizer.eos_token_id
+        input_ids = tokenizer(prompt, return_tensors="pt", padding=True, pad_to_multiple_of=8)["input_ids"]
+        tokenizer.padding_side = old
+    input_ids = input_ids.to(device)
+    b, n = input_ids.shape
+    cuda = torch.device(device).type == "cuda"
+    dec = StaticGraphDecoder(model, b, n + int(max_new_tokens) + 8, device=device)
+
+    for _ in range(max(1, int(warmups))):
+        dec.prefill(input_ids)
+    if cuda:
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        _, ttft = _cuda_event_ms(lambda: dec.prefill(input_ids))
+    else:
+        s = time.perf_counter()
+        dec.prefill(input_ids)
+        ttft = (time.perf_counter() - s) * 1000
+    if cuda and use_cuda_graph:
+        dec.capture()
+
+    def run():
+        first = dec.prefill(input_ids)
+        rest = dec.decode(int(max_new_tokens) - 1)
+        return torch.cat([first, rest], 1)
+
+    for _ in range(max(1, int(warmups))):
+        run()
+    if cuda:
+        torch.cuda.synchronize()
+        out, total_ms = _cuda_event_ms(run)
+        torch.cuda.synchronize()
+    else:
+        s = time.perf_counter()
+        out = run()
+        total_ms = (time.perf_counter() - s) * 1000
+    generated = int(out.shape[1])
+    decode_ms = max(0.001, total_ms - ttft)
+    res = dict(prompt_tokens=n, generated_tokens=generated, ttft_ms=ttft,
+               decode_tokens_s=b * generated / (decode_ms / 1000.0), total_tokens_s=b * generated / (total_ms / 1000.0),
+               batch=b, tokens=out)
+    if cuda:
+        res.update(peak_vram_gb=torch.cuda.max_memory_allocated() / 1024 ** 3,
+                   current_vram_gb=torch.cuda.memory_allocated() / 1024 ** 3,
+                   reserved_vram_gb=torch.cuda.memory_reserved() / 1024 ** 3)
+    return res
