@@ -1,0 +1,181 @@
+"""Random-init decoder models with seeded mixed-bit plans, for whole-model decode measurements.
+
+Mirrors what the reference's model benchmark does around the hot path (module swap:
+``ai_accel_lab/model_benchmark.py:83-103``; plan application: ``ai_accel_lab/optimize/bundle.py:34-47``)
+without checkpoints or tokenizers: the benchmark configurations specify random-init weights
+N(0, 0.02), a seeded per-Linear bit-width plan, group 128, 1 % outlier columns and rank-8
+residual factors given directly (an SVD per layer of an 8B/70B model is not affordable and not
+what is being measured).
+
+Tensor parallelism: every rank builds a *local* model whose attention heads and MLP width are
+divided by the world size (row shards of q/k/v/gate/up, column shards of o/down) and wraps
+o_proj / down_proj in ``AllReduceLinear``.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+from torch import nn
+
+from .optimize import HybridInt2Linear, HybridInt4Linear
+from .optimize._hybrid_base import snap_outlier_count
+from .kernels.groupwise_int2 import pack_groupwise_int2
+from .kernels.groupwise_int4 import pack_groupwise_int4
+from .tp import AllReduceLinear
+
+TARGETS = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+COLUMN_SPLIT = ("o_proj", "down_proj")
+
+SHAPES = {
+    "qwen2.5-0.5b": dict(family="qwen2", layers=24, hidden=896, inter=4864, heads=14, kv_heads=2, head_dim=64,
+                         vocab=151936, qkv_bias=True),
+    "llama-3-8b": dict(family="llama", layers=32, hidden=4096, inter=14336, heads=32, kv_heads=8, head_dim=128,
+                       vocab=128256, qkv_bias=False),
+    "llama-3-70b": dict(family="llama", layers=80, hidden=8192, inter=28672, heads=64, kv_heads=8, head_dim=128,
+                        vocab=128256, qkv_bias=False),
+}
+
+
+def local_config(shape: str, world: int = 1, layers: int | None = None, max_positions: int = 4096):
+    """HF config of one rank's slice of the model (world == 1: the whole model)."""
+    from transformers import LlamaConfig, Qwen2Config
+    s = SHAPES[shape]
+    if s["heads"] % world or s["kv_heads"] % world or s["inter"] % world:
+        raise ValueError(f"{shape} cannot be split {world} ways (heads {s['heads']}/{s['kv_heads']}, inter {s['inter']})")
+    kw = dict(hidden_size=s["hidden"], intermediate_size=s["inter"] // world,
+              num_hidden_layers=layers if layers is not None else s["layers"],
+              num_attention_heads=s["heads"] // world, num_key_value_heads=s["kv_heads"] // world,
+              head_dim=s["head_dim"], vocab_size=s["vocab"], max_position_embeddings=max_positions,
+              initializer_range=0.02, tie_word_embeddings=False)
+    if s["family"] == "qwen2":
+        cfg = Qwen2Config(**kw)
+    else:
+        cfg = LlamaConfig(attention_bias=False, mlp_bias=False, **kw)
+    return cfg
+
+
+def build_fp16_model(shape: str, device, world: int = 1, layers: int | None = None, seed: int = 0,
+                     max_positions: int = 4096):
+    """Random-init fp16 model (this rank's slice) on ``device``; o_proj / down_proj all-reduce when world > 1."""
+    from transformers import AutoModelForCausalLM
+    cfg = local_config(shape, world, layers, max_positions)
+    torch.manual_seed(seed)
+    with torch.device(device):
+        model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
+    model.eval()
+    if world > 1:
+        for name, mod in list(model.named_modules()):
+            if isinstance(mod, nn.Linear) and name.split(".")[-1] in COLUMN_SPLIT:
+                _set(model, name, AllReduceLinear(mod))
+    return model
+
+
+def _set(root, fqn, new):
+    parts = fqn.split(".")
+    obj = root
+    for p in parts[:-1]:
+        obj = getattr(obj, p)
+    setattr(obj, parts[-1], new)
+
+
+def target_linears(model):
+    """(fqn, module) of every Linear the reference's planners consider (lm_head is not one of them)."""
+    out = []
+    for name, mod in model.named_modules():
+        if name.split(".")[-1] not in TARGETS:
+            continue
+        if isinstance(mod, nn.Linear):
+            out.append((name, mod))
+        elif isinstance(mod, AllReduceLinear) and isinstance(mod.inner, nn.Linear):
+            out.append((name, mod.inner))
+    return out
+
+
+@dataclasses.dataclass
+class PlanEntry:
+    name: str
+    bits: int            # 2, 4 or 16
+    group_size: int
+    outlier_columns: int
+    residual_rank: int
+
+
+def seeded_plan(model, probs=(0.6, 0.3, 0.1), seed=0, group_size=128, outlier_frac=0.01, residual_rank=8,
+                global_k: dict | None = None):
+    """Per-Linear bit width drawn from ``probs`` = P(INT2), P(INT4), P(FP16) with a seeded generator.
+    The outlier count is ``int(outlier_frac * K)`` of the *unsharded* layer, snapped as the module
+    constructors do (``global_k`` maps a leaf name to the unsharded K when the model is a shard)."""
+    g = torch.Generator().manual_seed(seed)
+    names = [n for n, _ in target_linears(model)]
+    draws = torch.multinomial(torch.tensor(probs, dtype=torch.float), len(names), replacement=True, generator=g)
+    mods = dict(model.named_modules())
+    plan = []
+    for n, d in zip(names, draws.tolist()):
+        lin = mods[n].inner if isinstance(mods[n], AllReduceLinear) else mods[n]
+        k = lin.in_features
+        kg = (global_k or {}).get(n.split(".")[-1], k)
+        oc = snap_outlier_count(int(outlier_frac * kg), kg)
+        bits = (2, 4, 16)[d]
+        plan.append(PlanEntry(n, bits, group_size, min(oc, k), residual_rank if bits != 16 else 0))
+    return plan
+
+
+@torch.no_grad()
+def apply_plan(model, plan, seed=0):
+    """Swap the planned Linears for packed modules (quantised where the weight lives, GPU or CPU).
+    Residual factors are drawn N(0, 0.01) as the benchmark configurations specify."""
+    mods = dict(model.named_modules())
+    g = torch.Generator(device="cpu").manual_seed(seed + 1)
+    for e in plan:
+        if e.bits == 16:
+            continue
+        holder = mods[e.name]
+        lin = holder.inner if isinstance(holder, AllReduceLinear) else holder
+        cls = HybridInt2Linear if e.bits == 2 else HybridInt4Linear
+        new = cls(lin, e.group_size, None, e.outlier_columns)
+        if e.residual_rank:
+            u = torch.randn(lin.out_features, e.residual_rank, generator=g) * 0.01
+            v = torch.randn(e.residual_rank, lin.in_features, generator=g) * 0.01
+            new.set_residual(u.to(lin.weight.device), v.to(lin.weight.device))
+        new.graph_safe = True
+        if isinstance(holder, AllReduceLinear):
+            holder.inner = new
+        else:
+            _set(model, e.name, new)
+        lin.weight = None          # drop the dense source
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+    return model
+
+
+def linear_weight_bytes(model) -> dict:
+    """Bytes of Linear-layer weights one decoded token must read (packed + fp16, lm_head included)."""
+    packed = dense = 0
+    for _, mod in model.named_modules():
+        if isinstance(mod, (HybridInt2Linear, HybridInt4Linear)):
+            for t in (mod.packed, mod.scales, mod.outlier_weight, mod.res_u, mod.res_v, mod.bias):
+                if t is not None:
+                    packed += t.numel() * t.element_size()
+        elif isinstance(mod, nn.Linear) and mod.weight is not None:
+            dense += mod.weight.numel() * mod.weight.element_size()
+    return dict(packed_bytes=packed, fp16_bytes=dense, total=packed + dense)
+
+
+def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
+                     mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True):
+    """Build (this rank's slice of) the model, optionally apply the seeded mixed-bit plan, and run the
+    fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts."""
+    from .runtime_v5 import generate_static_benchmark
+    model = build_fp16_model(shape, device, world, layers, seed, max_positions=prompt_len + new_tokens + 16)
+    if mixed:
+        s = SHAPES[shape]
+        plan = seeded_plan(model, probs, seed, global_k={"o_proj": s["heads"] * s["head_dim"], "down_proj": s["inter"]})
+        apply_plan(model, plan, seed)
+    g = torch.Generator().manual_seed(seed + 7)
+    ids = torch.randint(0, SHAPES[shape]["vocab"], (batch, prompt_len), generator=g)
+    res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=new_tokens, device=device,
+                                    use_cuda_graph=use_cuda_graph)
+    res.update(linear_weight_bytes(model))
+    res["shape"], res["mixed"], res["world"] = shape, mixed, world
+    return res

@@ -64,6 +64,61 @@ class HybridPackedLinear(nn.Module):
         else:
             self.register_buffer("bias", source_bias.detach().to(torch.float16))
 
+    @classmethod
+    def from_buffers(cls, packed, scales, original_k: int, group_size: int, outlier_idx=None,
+                     outlier_weight=None, bias=None, res_u=None, res_v=None):
+        """Build a module directly from packed buffers (no source ``nn.Linear``): what a loader
+        that already holds a bundle's tensors, or a tensor-parallel sharder, needs.  ``cls`` must be
+        one of the concrete classes (it fixes the bit width)."""
+        if cls.bits not in (2, 4):
+            raise TypeError("call from_buffers on HybridInt2Linear or HybridInt4Linear")
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        n = int(packed.shape[0])
+        dev = packed.device
+        if outlier_idx is None or outlier_idx.numel() == 0:
+            outlier_idx = torch.empty(0, device=dev, dtype=torch.int32)
+            outlier_weight = torch.empty((n, 0), device=dev, dtype=torch.float16)
+        self.register_buffer("outlier_idx", outlier_idx.to(torch.int32))
+        self.register_buffer("outlier_weight", outlier_weight.to(torch.float16).contiguous())
+        self.register_buffer("packed", packed.contiguous())
+        self.register_buffer("scales", scales.to(torch.float16).contiguous())
+        self.original_k = int(original_k)
+        self.padded_k = int(packed.shape[1]) * (8 // cls.bits)
+        self.group_size = int(group_size)
+        self.in_features = int(original_k)
+        self.out_features = n
+        self.graph_safe = False
+        self.kernel = "auto"
+        self.backend = "auto"
+        if bias is None:
+            self.bias = None
+        else:
+            self.register_buffer("bias", bias.to(torch.float16))
+        self.residual_rank = 0
+        self.res_u = None
+        self.res_v = None
+        if res_u is not None and res_u.numel():
+            self.set_residual(res_u, res_v)
+        if packed.is_cuda:
+            from .. import ops
+            ops.ensure_workspace(packed.device)
+        return self
+
+    def set_residual(self, res_u: torch.Tensor, res_v: torch.Tensor) -> None:
+        """Attach given low-rank factors ``res_u [N,r]``, ``res_v [r,K]`` (replacing any present)."""
+        if res_u.shape[0] != self.out_features or res_v.shape[1] != self.in_features or res_u.shape[1] != res_v.shape[0]:
+            raise ValueError("res_u must be [N,r] and res_v [r,K]")
+        dev = self.packed.device
+        for name in ("res_u", "res_v"):
+            if name in self.__dict__:
+                del self.__dict__[name]     # plain None placeholders make way for buffers
+            if name in self._buffers:
+                del self._buffers[name]
+        self.register_buffer("res_u", res_u.detach().to(dev, torch.float16).contiguous())
+        self.register_buffer("res_v", res_v.detach().to(dev, torch.float16).contiguous())
+        self.residual_rank = int(res_u.shape[1])
+
     def _apply(self, fn, *args, **kwargs):
         out = super()._apply(fn, *args, **kwargs)
         if self.packed.is_cuda:

@@ -44,17 +44,5 @@ class HybridInt4Linear(HybridPackedLinear):
             uu, s, vh = torch.linalg.svd(w.float() - q, full_matrices=False)
             self.set_residual((uu[:, :rank] * s[:rank]), vh[:rank, :])
 
-    def set_residual(self, res_u: torch.Tensor, res_v: torch.Tensor) -> None:
-        """Attach given low-rank factors (``[N,r]``, ``[r,K]``)."""
-        if res_u.shape[0] != self.out_features or res_v.shape[1] != self.in_features or res_u.shape[1] != res_v.shape[0]:
-            raise ValueError("res_u must be [N,r] and res_v [r,K]")
-        dev = self.packed.device
-        for name in ("res_u", "res_v"):
-            if name in self.__dict__:
-                del self.__dict__[name]     # plain None placeholders make way for buffers
-        self.register_buffer("res_u", res_u.detach().to(dev, torch.float16).contiguous())
-        self.register_buffer("res_v", res_v.detach().to(dev, torch.float16).contiguous())
-        self.residual_rank = int(res_u.shape[1])
-
     def packed_weight(self) -> GroupwiseInt4Weight:
         return GroupwiseInt4Weight(self.packed, self.scales, self.original_k, self.padded_k, self.group_size, True)

@@ -1,0 +1,62 @@
+"""Model-level host logic on the CPU: local (sharded) configs, seeded plans, module swap, and the
+static-cache greedy decoder against Hugging Face's own generate()."""
+import pytest
+import torch
+
+from ai_accel_studio_b200 import model_tools as mt
+from ai_accel_studio_b200.optimize import HybridInt2Linear, HybridInt4Linear
+from ai_accel_studio_b200.runtime_v5 import StaticGraphDecoder, generate_static_benchmark
+from ai_accel_studio_b200.tp import AllReduceLinear
+
+
+@pytest.fixture()
+def tiny(monkeypatch):
+    monkeypatch.setitem(mt.SHAPES, "tiny", dict(family="llama", layers=2, hidden=256, inter=512, heads=4, kv_heads=2,
+                                                head_dim=64, vocab=320, qkv_bias=False))
+    return "tiny"
+
+
+def test_local_config_shards_heads_and_mlp(tiny):
+    c1, c2 = mt.local_config(tiny, 1), mt.local_config(tiny, 2)
+    assert (c2.num_attention_heads, c2.num_key_value_heads, c2.intermediate_size) == (2, 1, 256)
+    assert c2.hidden_size == c1.hidden_size == 256 and c2.head_dim == 64
+    with pytest.raises(ValueError):
+        mt.local_config(tiny, 4)                     # 2 kv heads cannot be split 4 ways
+    cfg = mt.local_config("llama-3-70b", 8)
+    assert (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size) == (8, 1, 3584)
+
+
+def test_seeded_plan_and_swap(tiny):
+    model = mt.build_fp16_model(tiny, "cpu", world=2)
+    assert sum(isinstance(m, AllReduceLinear) for m in model.modules()) == 4      # o_proj + down_proj, 2 layers
+    plan = mt.seeded_plan(model, (0.6, 0.3, 0.1), seed=5, global_k={"o_proj": 256, "down_proj": 512})
+    again = mt.seeded_plan(model, (0.6, 0.3, 0.1), seed=5, global_k={"o_proj": 256, "down_proj": 512})
+    assert [(e.name, e.bits) for e in plan] == [(e.name, e.bits) for e in again]
+    assert len(plan) == 14 and {e.bits for e in plan} <= {2, 4, 16}
+    mt.apply_plan(model, plan)
+    mods = dict(model.named_modules())
+    for e in plan:
+        m = mods[e.name]
+        m = m.inner if isinstance(m, AllReduceLinear) else m
+        if e.bits == 2:
+            assert isinstance(m, HybridInt2Linear) and m.residual_rank == 8 and m.group_size == 128
+        elif e.bits == 4:
+            assert isinstance(m, HybridInt4Linear) and m.residual_rank == 8
+        else:
+            assert isinstance(m, torch.nn.Linear)
+    b = mt.linear_weight_bytes(model)
+    assert b["packed_bytes"] > 0 and b["fp16_bytes"] > 0
+
+
+def test_static_decoder_matches_hf_generate(tiny):
+    model = mt.build_fp16_model(tiny, "cpu").float()
+    ids = torch.randint(0, 320, (2, 9), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = model.generate(ids, do_sample=False, max_new_tokens=6, min_new_tokens=6, cache_implementation="static",
+                             pad_token_id=0)[:, 9:]
+    dec = StaticGraphDecoder(model, 2, 32, device="cpu")
+    first = dec.prefill(ids)
+    rest = dec.decode(5)
+    assert torch.equal(torch.cat([first, rest], 1), ref)
+    res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=6, device="cpu", warmups=1)
+    assert torch.equal(res["tokens"], ref) and res["generated_tokens"] == 6 and res["decode_tokens_s"] > 0
