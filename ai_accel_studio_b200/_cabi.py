@@ -17,7 +17,7 @@ KERNEL = {"auto": 0, "simt": 1, "mma": 2}
 MAX_M = 4
 ABI_VERSION = 1
 
-EXPORTS = ("qgemv_run", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
+EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem")
 
 
@@ -61,6 +61,8 @@ def lib():
     l = C.CDLL(str(LIB_PATH))
     l.qgemv_run.argtypes = [C.POINTER(Problem), C.c_void_p]
     l.qgemv_run.restype = C.c_int
+    l.qgemv_run_static.argtypes = [C.POINTER(Problem), C.c_void_p]
+    l.qgemv_run_static.restype = C.c_int
     l.qgemv_workspace_bytes.argtypes = [C.c_int] * 6
     l.qgemv_workspace_bytes.restype = C.c_size_t
     l.qgemv_plan_name.argtypes = [C.POINTER(Problem)]
@@ -99,6 +101,11 @@ def workspace_bytes(bits: int, m: int, n: int, k_padded: int, group: int, rank: 
 
 def run(problem: Problem, stream: int) -> None:
     check(lib().qgemv_run(C.byref(problem), C.c_void_p(stream)))
+
+
+def run_static(problem: Problem, stream: int) -> None:
+    """``qgemv_run_static``: the library's built-in scratch instead of a caller workspace."""
+    check(lib().qgemv_run_static(C.byref(problem), C.c_void_p(stream)))
 
 
 def plan_name(problem: Problem):

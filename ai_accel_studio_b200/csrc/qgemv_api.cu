@@ -38,7 +38,7 @@ int simt_unit_bytes(const qgemv_problem& p) {
     return 1;
 }
 
-int validate(const qgemv_problem* p) {
+int validate(const qgemv_problem* p, size_t need) {
     if (!p) { set_error("qgemv_run: problem is NULL"); return QGEMV_ERR_BAD_ARG; }
     if (p->bits != 2 && p->bits != 4) { set_error("qgemv_run: bits must be 2 or 4 (got %d)", p->bits); return QGEMV_ERR_BAD_ARG; }
     if (p->m < 1 || p->m > QGEMV_MAX_M) { set_error("qgemv_run: M must be 1..%d (got %d); larger batches use the dequantise + GEMM path", QGEMV_MAX_M, p->m); return QGEMV_ERR_BAD_ARG; }
@@ -56,7 +56,6 @@ int validate(const qgemv_problem* p) {
     if (p->outliers > 0 && p->ldow < p->outliers) { set_error("qgemv_run: ldow < outliers"); return QGEMV_ERR_SHAPE; }
     if (p->rank > 0 && (p->ldu < p->rank || p->ldv < p->k_original)) { set_error("qgemv_run: ldu < rank or ldv < k_original"); return QGEMV_ERR_SHAPE; }
     if (!aligned(p->x, 2) || !aligned(p->y, 2) || !aligned(p->scales, 2)) { set_error("qgemv_run: 16-bit tensors must be 2-byte aligned"); return QGEMV_ERR_ALIGN; }
-    const size_t need = qgemv_workspace_bytes(p->bits, p->m, p->n, p->k_padded, p->group, p->rank);
     if (!p->workspace || p->workspace_bytes < need) { set_error("qgemv_run: workspace of %zu bytes required (got %zu)", need, p->workspace ? p->workspace_bytes : (size_t)0); return QGEMV_ERR_WORKSPACE; }
     if (!aligned(p->workspace, 256)) { set_error("qgemv_run: workspace must be 256-byte aligned"); return QGEMV_ERR_ALIGN; }
     return QGEMV_OK;
@@ -102,17 +101,21 @@ extern "C" size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, in
 }
 
 extern "C" const char* qgemv_plan_name(const qgemv_problem* p) {
-    if (validate(p) != QGEMV_OK) return nullptr;
+    if (validate(p, qgemv_workspace_bytes(0, 0, 0, 0, 0, 0)) != QGEMV_OK) return nullptr;
     if (p->kernel != QGEMV_KERNEL_SIMT) {
-        const MmaPlan plan = plan_mma(*p);
+        const MmaPlan plan = plan_mma(*p, kMaxPartialFloats);
         if (plan.ok) return plan.name;
         if (p->kernel == QGEMV_KERNEL_MMA) return nullptr;
     }
     return simt_name(p->bits, p->m, simt_unit_bytes(*p));
 }
 
-extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
-    const int v = validate(p);
+namespace {
+
+// Validate, pick a kernel, launch.  `partial_floats` is the capacity of the partial-sum area of
+// the workspace the problem points at.
+int run_checked(const qgemv_problem* p, void* stream, size_t need_bytes, size_t partial_floats) {
+    const int v = validate(p, need_bytes);
     if (v != QGEMV_OK) return v;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Args a = make_args(*p);
@@ -121,7 +124,7 @@ extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
     MmaPlan plan{};
     bool use_mma = false;
     if (p->kernel != QGEMV_KERNEL_SIMT) {
-        plan = plan_mma(*p);
+        plan = plan_mma(*p, partial_floats);
         use_mma = plan.ok;
         if (!use_mma && p->kernel == QGEMV_KERNEL_MMA) {
             set_error("qgemv_run: the tensor-core-assisted kernel does not support this shape "
@@ -136,4 +139,62 @@ extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
     }
     if (use_mma) return launch_mma(a, p->bits, bf16, plan, s);
     return launch_simt(a, p->bits, bf16, simt_unit_bytes(*p), s);
+}
+
+// ---- scratch for callers that cannot allocate ---------------------------------------------------
+// Same layout as a caller-provided workspace, with a smaller partial-sum area: enough for a
+// persistent grid of up to 256 CTAs (a B200 has 148 SMs).  Lives in every device that loads the
+// library until the process exits; zero-initialised when the module is loaded.
+constexpr size_t kStaticPartialFloats = 65536;
+constexpr size_t kStaticScratchBytes = kWsPartialOff + kStaticPartialFloats * sizeof(float);   // 328 704 bytes
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+}  // namespace
+
+extern "C" int qgemv_run_static(const qgemv_problem* p, void* stream) {
+    if (!p) { set_error("qgemv_run_static: problem is NULL"); return QGEMV_ERR_BAD_ARG; }
+    if ((long long)p->n > (long long)QGEMV_STATIC_MAX_N) {
+        set_error("qgemv_run_static: N = %d exceeds the built-in scratch's limit of %d rows; "
+                  "use qgemv_run with a caller-provided workspace", p->n, QGEMV_STATIC_MAX_N);
+        return QGEMV_ERR_TOO_LARGE;
+    }
+    if (p->rank > kMaxRank) {
+        set_error("qgemv_run_static: residual rank %d exceeds the limit of %d", p->rank, kMaxRank);
+        return QGEMV_ERR_TOO_LARGE;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        set_error("qgemv_run_static: no current CUDA device (or device ordinal >= %d)", kMaxDevices);
+        return QGEMV_ERR_LAUNCH;
+    }
+    if (!g_static_scratch_addr[dev]) {
+        // One-time set-up on this device: the symbol's name is only a host-side handle, the kernels
+        // need its device address.  Also puts the arrival counters into their required state.
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            (void)cudaGetLastError();
+            set_error("qgemv_run_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return QGEMV_ERR_LAUNCH;
+        }
+        const cudaError_t m = cudaMemsetAsync(ptr, 0, kWsPartialOff, static_cast<cudaStream_t>(stream));
+        if (m != cudaSuccess) {
+            (void)cudaGetLastError();
+            set_error("qgemv_run_static: clearing the scratch counters failed: %s", cudaGetErrorString(m));
+            return QGEMV_ERR_LAUNCH;
+        }
+        g_static_scratch_addr[dev] = ptr;
+    }
+    qgemv_problem q = *p;
+    q.workspace = g_static_scratch_addr[dev];
+    q.workspace_bytes = kStaticScratchBytes;
+    return run_checked(&q, stream, kStaticScratchBytes, kStaticPartialFloats);
+}
+
+extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
+    return run_checked(p, stream, qgemv_workspace_bytes(0, 0, 0, 0, 0, 0), kMaxPartialFloats);
 }

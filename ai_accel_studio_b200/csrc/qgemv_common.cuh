@@ -81,7 +81,7 @@ struct MmaPlan {
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
     const char* name;
 };
-MmaPlan plan_mma(const qgemv_problem& p);
+MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats);
 int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& plan, cudaStream_t s);
 
 }  // namespace qgemv

@@ -764,7 +764,7 @@ int launch_gb(const MmaArgs& p, int gb, bool bf16, int grid, int smem, cudaStrea
 
 }  // namespace
 
-MmaPlan plan_mma(const qgemv_problem& p) {
+MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     MmaPlan pl{};
     pl.ok = false;
     const int gb = p.group * p.bits / 8;
@@ -802,7 +802,7 @@ MmaPlan plan_mma(const qgemv_problem& p) {
     }
     if (pl.tile_aligned) slot_cap = ((pl.nt + grid - 1) / grid) * rpt;
     if (slot_cap * slot_bytes > 65536) return pl;
-    if ((size_t)grid * 2 * 4 * 32 > kMaxPartialFloats) return pl;
+    if ((size_t)grid * 2 * 4 * 32 > partial_floats) return pl;
     pl.scales_async = (p.lds % cg == 0) && al(p.scales, (size_t)cg * 2) ? 1 : 0;
     pl.ocb = align_up(p.outliers * 2, 16);
     pl.rb = align_up(p.rank * 2, 16);

@@ -92,6 +92,24 @@ typedef struct qgemv_problem {
  *           (packed_dense_kernel<0>, csrc/packed_kernels_cuda.cu:27-83). */
 int qgemv_run(const qgemv_problem* p, void* stream);
 
+/* The same fused GEMV for callers that may not allocate device memory (code running under a
+ * memory budget fixed at start-up, inside somebody else's allocator-free plugin hook, or in a
+ * process whose only device buffers are the ones handed to it): p->workspace and
+ * p->workspace_bytes are ignored and a scratch area built into the library is used instead.
+ * It has no counterpart in the reference project.
+ *
+ *  - The scratch is a fixed 328 704-byte array in device memory that every GPU which loads the
+ *    library carries until the process exits.  It serves problems with N <= QGEMV_STATIC_MAX_N
+ *    and rank <= 64; anything larger is refused with QGEMV_ERR_TOO_LARGE.
+ *  - The first call on each device (with that device current) looks up the array's device address
+ *    and clears its counters on `stream`; make that first call before starting a stream capture.
+ *    Later calls only launch kernels.  No call allocates or frees anything.
+ *  - All calls on a device share the one array, and it keeps what the last call left in it.
+ *    Calls that can overlap on the GPU (different streams without ordering) would race on it:
+ *    serialise them, or use qgemv_run with separate workspaces. */
+#define QGEMV_STATIC_MAX_N 262128
+int qgemv_run_static(const qgemv_problem* p, void* stream);
+
 /* Bytes of workspace qgemv_run needs for a problem of this shape (never 0; at most a few MB). */
 size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, int group, int rank);
 
