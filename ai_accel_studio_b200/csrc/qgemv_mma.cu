@@ -40,6 +40,10 @@
 namespace qgemv {
 namespace {
 
+#ifndef QGEMV_MAX_WARPS
+#define QGEMV_MAX_WARPS 16
+#endif
+constexpr int kMaxWarps = QGEMV_MAX_WARPS;   // warps per CTA the kernel is compiled for (register budget = 65536 / (32 * warps))
 constexpr int kTileRows = 16;          // weight rows per mma tile (one warp owns one tile at a time)
 constexpr int kMaxOutliers = 256;      // outlier activations staged in shared memory
 
@@ -83,17 +87,41 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
-__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
-    if (pending >= 3) cp_async_wait<3>();
-    else if (pending == 2) cp_async_wait<2>();
-    else if (pending == 1) cp_async_wait<1>();
-    else cp_async_wait<0>();
-}
+// Ring depth per warp is a compile-time constant so that the wait depth is an immediate.
+constexpr int kStages = 4;
+
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Same with a zero addend: starts an accumulation chain without clearing registers first.
+__device__ __forceinline__ void mma_f16_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+// Explicit shared-window loads / stores (32-bit addresses).  volatile: they stay ordered with the
+// asynchronous-copy waits, which are volatile too.
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+    float2 v; asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a)); return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+    float4 v; asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a)); return v;
+}
+__device__ __forceinline__ void sts128f(uint32_t a, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 // Programmatic dependent launch: let the next kernel in the stream begin its prologue now, and
 // block until the kernels this one depends on have completed and flushed their writes.
@@ -396,7 +424,7 @@ __device__ __forceinline__ int owner_of(int u, int units, int parts) {
 // The kernel.  Persistent grid, blockDim.x = 32 * nw; every warp is its own producer and consumer.
 // ---------------------------------------------------------------------------------------------
 template <int BITS, int GB, int M, bool BF16>
-__global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant__ MmaArgs p) {
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __grid_constant__ MmaArgs p) {
     using GE = Geo<BITS, GB>;
     constexpr int TT = (M + 1) / 2;                   // quad lanes that hold useful output columns
     constexpr int SLOT_BYTES = 8 * TT * 16;           // one run's partial sums in shared memory
@@ -414,7 +442,7 @@ __global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant
     const int r1 = p.tile_aligned ? first_unit(cta + 1, p.nt, grid) * p.rpt : first_unit(cta + 1, p.runs, grid);
     const int T0 = r0 / p.rpt, T1 = (r1 - 1) / p.rpt;
 
-    unsigned char* ring = smem + p.off_ring + (size_t)warp * p.stages * GE::STAGE_BYTES;
+    unsigned char* ring = smem + p.off_ring + (size_t)warp * kStages * GE::STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring);
     int4* meta = reinterpret_cast<int4*>(smem + p.off_meta) + warp * 4;      // per stage: tile, chunk, slot, last
     unsigned char* epi = smem + p.off_epi + (size_t)warp * p.epi_bytes;
@@ -462,15 +490,23 @@ __global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant
         }
         if (pf_run >= 0) {
             const int ngr = min(GE::CG, p.ng - pf_ch * GE::CG);
-            const int pieces = (ngr * GB) >> 4;
             const uint32_t sbase = ring_u32 + s * GE::STAGE_BYTES;
             const bool edge = ragged_n && pf_tile == p.nt - 1;        // rows past N are clamped to the last row
-            if (lcol < pieces) {
-                if (!edge) {
-                    const uint8_t* src = lane_src + (size_t)pf_tile * tile_stride + (size_t)pf_ch * GE::CB;
+            if (ngr == GE::CG && !edge && p.scales_async) {
+                // common case, straight-line: 4 row-group copies by every lane + one scale copy by lanes 0..15
+                const uint8_t* src = lane_src + (size_t)pf_tile * tile_stride + (size_t)pf_ch * GE::CB;
 #pragma unroll
-                    for (int it = 0; it < NIT; ++it) cp_async16(sbase + dst_off[it], src + it * it_stride);
-                } else {
+                for (int it = 0; it < NIT; ++it) { cp_async16(sbase + dst_off[it], src); src += it_stride; }
+                const __half* ssrc = lane_sc + (size_t)pf_tile * sc_tile_stride + pf_ch * GE::CG;
+                const uint32_t sdst = sbase + GE::SCALE_OFF + lane * 16;
+                if (lane < kTileRows) {
+                    if constexpr (GE::CG == 8) cp_async16(sdst, ssrc);
+                    else if constexpr (GE::CG == 4) cp_async8(sdst, ssrc);
+                    else cp_async4(sdst, ssrc);
+                }
+            } else {
+                const int pieces = (ngr * GB) >> 4;
+                if (lcol < pieces) {
                     const uint8_t* src = a.packed + (size_t)pf_ch * GE::CB + lcol * 16;
 #pragma unroll
                     for (int it = 0; it < NIT; ++it) {
@@ -478,18 +514,17 @@ __global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant
                         cp_async16(sbase + dst_off[it], src + (size_t)row * a.ldp);
                     }
                 }
-            }
-            if (lane < kTileRows) {                   // this row's scales for the chunk
-                const __half* src = edge ? a.scales + (size_t)min(pf_tile * kTileRows + lane, a.n - 1) * a.lds + pf_ch * GE::CG
-                                         : lane_sc + (size_t)pf_tile * sc_tile_stride + pf_ch * GE::CG;
-                const uint32_t dst = sbase + GE::SCALE_OFF + lane * 16;
-                if (p.scales_async && ngr == GE::CG) {
-                    if constexpr (GE::CG == 8) cp_async16(dst, src);
-                    else if constexpr (GE::CG == 4) cp_async8(dst, src);
-                    else cp_async4(dst, src);
-                } else {
-                    __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16);
-                    for (int i = 0; i < ngr; ++i) d[i] = __ldg(src + i);
+                if (lane < kTileRows) {                   // this row's scales for the chunk
+                    const __half* src = a.scales + (size_t)min(pf_tile * kTileRows + lane, a.n - 1) * a.lds + pf_ch * GE::CG;
+                    if (p.scales_async && ngr == GE::CG) {
+                        const uint32_t dst = sbase + GE::SCALE_OFF + lane * 16;
+                        if constexpr (GE::CG == 8) cp_async16(dst, src);
+                        else if constexpr (GE::CG == 4) cp_async8(dst, src);
+                        else cp_async4(dst, src);
+                    } else {
+                        __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16);
+                        for (int i = 0; i < ngr; ++i) d[i] = __ldg(src + i);
+                    }
                 }
             }
             if (lane == 0) meta[s] = make_int4(pf_tile, pf_ch, pf_run - r0, pf_ch + 1 == pf_end);
@@ -527,111 +562,119 @@ __global__ void __launch_bounds__(512, 1) qgemv_mma_kernel(const __grid_constant
         issue_next(0);                                // the rest of the ring is filled while computing: a warp that
         QTRACE(1);                                    // queued it all here would sit behind its own copies
     });
-    issue_next(1);
+    for (int s = 1; s < kStages; ++s) issue_next(s);
     __syncthreads();                                  // staged activations visible to every warp
     QTRACE(2);
 
-    const float2* gx = reinterpret_cast<const float2*>(smem + p.off_gx);
-    const uint4* xs16 = reinterpret_cast<const uint4*>(smem + p.off_xs);
-    const uint4* xs_lane = xs16 + g * 4 + t;
     const int ma = min(2 * t, M - 1), mb = min(2 * t + 1, M - 1);
     unsigned char* slots = smem + p.off_slots;
 
     // ---- consumer side ------------------------------------------------------------------------
-    float y[4] = {0.f, 0.f, 0.f, 0.f};
-    int stage = 0;                              // slot being consumed
-    int fill = p.stages > 2 ? 2 : 0;            // next slot to fill (two copies are already queued)
-    int ahead = 2;                              // copies queued and not yet consumed
-    bool first = true;
-    for (;;) {
-        // Top the ring up, at most two copies per iteration, so that the ramp-up is spread over
-        // the first iterations instead of blocking every warp before it computes anything.
-        for (int k = 0; k < 2 && ahead < p.stages; ++k) {
-            issue_next(fill);
-            fill = fill + 1 == p.stages ? 0 : fill + 1;
-            ++ahead;
-        }
-        cp_async_wait_dyn(ahead - 1);           // everything but the newest ahead-1 groups is done: this slot has landed
-        __syncwarp();
-        const int4 mt = meta[stage];
-        if (mt.x < 0) break;
-        if (first) { QTRACE(3); first = false; }
-        const int ch = mt.y;
-        const int ngr = min(GE::CG, p.ng - ch * GE::CG);
-        const unsigned char* sb = ring + stage * GE::STAGE_BYTES;
-        const unsigned char* row0 = sb + g * GE::PITCH;            // rows g and g+8 share the swizzle
-        const unsigned char* row1 = row0 + 8 * GE::PITCH;
-        const int sw = GE::swz(g);
-        __align__(16) __half sc0[8], sc1[8];
-        if constexpr (GE::CG == 8) {
-            *reinterpret_cast<uint4*>(sc0) = *reinterpret_cast<const uint4*>(sb + GE::SCALE_OFF + g * 16);
-            *reinterpret_cast<uint4*>(sc1) = *reinterpret_cast<const uint4*>(sb + GE::SCALE_OFF + (g + 8) * 16);
-        } else if constexpr (GE::CG == 4) {
-            *reinterpret_cast<uint2*>(sc0) = *reinterpret_cast<const uint2*>(sb + GE::SCALE_OFF + g * 16);
-            *reinterpret_cast<uint2*>(sc1) = *reinterpret_cast<const uint2*>(sb + GE::SCALE_OFF + (g + 8) * 16);
+    // Shared-memory operands are addressed through the 32-bit shared window with explicit
+    // ld.shared instructions: the compiler then folds every compile-time offset into the
+    // instruction and no 64-bit address arithmetic is left in the loop.
+    // Lanes g >= M feed B columns whose results are never read: they load row M-1 instead of zeros.
+    const uint32_t xs_lane_u32 = smem_u32(smem + p.off_xs) + (min(g, M - 1) * 4 + t) * 16;
+    const uint32_t gx_lane_u32 = smem_u32(smem + p.off_gx) + (M % 2 == 0 ? (M >= 2 ? min(2 * t, M - 2) : 0) : 0) * 8;
+    const uint32_t gx_a_u32 = smem_u32(smem + p.off_gx) + ma * 8, gx_b_u32 = smem_u32(smem + p.off_gx) + mb * 8;
+    const uint32_t slots_u32 = smem_u32(slots) + (g * TT + t) * 16;
+    const uint32_t meta_u32 = smem_u32(meta);
+    const int sw16 = GE::swz(g) << 4;
+    const uint32_t lane_row_u32 = ring_u32 + g * GE::PITCH;         // row g of slot 0 (row g+8 is 8 rows further)
+    const uint32_t lane_sc_u32 = ring_u32 + GE::SCALE_OFF + g * 16;
+    const int ng_total = p.ng;
+    constexpr int GSTRIDE = GE::TW * (GE::NCLS / 2) * M * 4 * 16;    // bytes of staged x per group
+
+    // One group of one chunk: G = absolute group index, gi = group inside the chunk.
+    auto do_group = [&](uint32_t rowa, uint32_t rowb, int gi, int G, float s0, float s1, float (&yy)[4]) {
+        const int lo = gi * GB + t * GE::TB;                          // logical byte offset of this lane's bytes
+        const uint32_t off = (uint32_t)(((lo & ~15) ^ sw16) + (lo & 15));
+        uint32_t w0[GE::TW], w1[GE::TW];
+        if constexpr (GE::TW == 1) {
+            w0[0] = lds32(rowa + off); w1[0] = lds32(rowb + off);
+        } else if constexpr (GE::TW == 2) {
+            const uint2 v0 = lds64(rowa + off), v1 = lds64(rowb + off);
+            w0[0] = v0.x; w0[1] = v0.y; w1[0] = v1.x; w1[1] = v1.y;
         } else {
-            *reinterpret_cast<uint32_t*>(sc0) = *reinterpret_cast<const uint32_t*>(sb + GE::SCALE_OFF + g * 16);
-            *reinterpret_cast<uint32_t*>(sc1) = *reinterpret_cast<const uint32_t*>(sb + GE::SCALE_OFF + (g + 8) * 16);
+            const uint4 v0 = lds128(rowa + off), v1 = lds128(rowb + off);
+            w0[0] = v0.x; w0[1] = v0.y; w0[2] = v0.z; w0[3] = v0.w;
+            w1[0] = v1.x; w1[1] = v1.y; w1[2] = v1.z; w1[3] = v1.w;
         }
+        const uint32_t xg = xs_lane_u32 + (uint32_t)G * GSTRIDE;
+        uint4 b[GE::TW * (GE::NCLS / 2)];
 #pragma unroll
-        for (int gi = 0; gi < GE::CG; ++gi) {
-            if (gi < ngr) {
-                const int G = ch * GE::CG + gi;
-                uint32_t w0[GE::TW], w1[GE::TW];
-                // logical byte offset of this lane's TB bytes -> swizzled 16-byte piece + offset in it
-                const int lo = gi * GB + t * GE::TB;
-                const int off = (((lo >> 4) ^ sw) << 4) + (lo & 15);
-                if constexpr (GE::TW == 1) {
-                    w0[0] = *reinterpret_cast<const uint32_t*>(row0 + off);
-                    w1[0] = *reinterpret_cast<const uint32_t*>(row1 + off);
-                } else if constexpr (GE::TW == 2) {
-                    const uint2 v0 = *reinterpret_cast<const uint2*>(row0 + off);
-                    const uint2 v1 = *reinterpret_cast<const uint2*>(row1 + off);
-                    w0[0] = v0.x; w0[1] = v0.y; w1[0] = v1.x; w1[1] = v1.y;
+        for (int q = 0; q < GE::TW * (GE::NCLS / 2); ++q) b[q] = lds128(xg + q * (M * 4 * 16));
+        float2 ga, gb;
+        if constexpr (M % 2 == 0) {
+            const float4 gq = lds128f(gx_lane_u32 + (uint32_t)G * (M * 8));
+            ga = make_float2(gq.x, gq.y); gb = make_float2(gq.z, gq.w);
+        } else {
+            ga = lds64f(gx_a_u32 + (uint32_t)G * (M * 8)); gb = lds64f(gx_b_u32 + (uint32_t)G * (M * 8));
+        }
+        // two independent accumulator chains (the classes alternate between them); the first
+        // instruction of each chain takes zero as its addend, so nothing has to be cleared
+        float accA[4], accB[4];
+#pragma unroll
+        for (int i = 0; i < GE::TW; ++i) {
+            const uint32_t h0 = w0[i] >> 8, h1 = w1[i] >> 8;
+#pragma unroll
+            for (int cp = 0; cp < GE::NCLS / 2; ++cp) {
+                const uint4 bb = b[i * (GE::NCLS / 2) + cp];
+                constexpr uint32_t MK = GE::MASK;
+                const uint32_t m0 = MK << (BITS * (2 * cp)), m1 = MK << (BITS * (2 * cp + 1));
+                if (i == 0 && cp == 0) {
+                    mma_f16_first(accA, w0[i] & m0, w1[i] & m0, h0 & m0, h1 & m0, bb.x, bb.y);
+                    mma_f16_first(accB, w0[i] & m1, w1[i] & m1, h0 & m1, h1 & m1, bb.z, bb.w);
                 } else {
-                    const uint4 v0 = *reinterpret_cast<const uint4*>(row0 + off);
-                    const uint4 v1 = *reinterpret_cast<const uint4*>(row1 + off);
-                    w0[0] = v0.x; w0[1] = v0.y; w0[2] = v0.z; w0[3] = v0.w;
-                    w1[0] = v1.x; w1[1] = v1.y; w1[2] = v1.z; w1[3] = v1.w;
+                    mma_f16(accA, w0[i] & m0, w1[i] & m0, h0 & m0, h1 & m0, bb.x, bb.y);
+                    mma_f16(accB, w0[i] & m1, w1[i] & m1, h0 & m1, h1 & m1, bb.z, bb.w);
                 }
-                // two independent accumulator chains (the classes alternate between them)
-                float accA[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint4* xg = xs_lane + G * (GE::TW * (GE::NCLS / 2) * M * 4);
-#pragma unroll
-                for (int i = 0; i < GE::TW; ++i) {
-                    const uint32_t h0 = w0[i] >> 8, h1 = w1[i] >> 8;
-#pragma unroll
-                    for (int cp = 0; cp < GE::NCLS / 2; ++cp) {
-                        uint4 b = make_uint4(0u, 0u, 0u, 0u);
-                        if (g < M) b = xg[(i * (GE::NCLS / 2) + cp) * M * 4];
-                        constexpr uint32_t MK = GE::MASK;
-                        const uint32_t m0 = MK << (BITS * (2 * cp)), m1 = MK << (BITS * (2 * cp + 1));
-                        mma_f16(accA, w0[i] & m0, w1[i] & m0, h0 & m0, h1 & m0, b.x, b.y);
-                        mma_f16(accB, w0[i] & m1, w1[i] & m1, h0 & m1, h1 & m1, b.z, b.w);
-                    }
-                }
-                const float s0 = __half2float(sc0[gi]), s1 = __half2float(sc1[gi]);
-                float2 ga, gb;
-                if constexpr (M % 2 == 0) {           // the two columns of this lane are neighbours: one 16-byte read
-                    const float4 gq = *reinterpret_cast<const float4*>(gx + G * M + (M >= 2 ? min(2 * t, M - 2) : 0));
-                    ga = make_float2(gq.x, gq.y); gb = make_float2(gq.z, gq.w);
-                } else {
-                    ga = gx[G * M + ma]; gb = gx[G * M + mb];
-                }
-                y[0] = fmaf(s0, fmaf(ga.y, accA[0] + accB[0], -ga.x), y[0]);
-                y[1] = fmaf(s0, fmaf(gb.y, accA[1] + accB[1], -gb.x), y[1]);
-                y[2] = fmaf(s1, fmaf(ga.y, accA[2] + accB[2], -ga.x), y[2]);
-                y[3] = fmaf(s1, fmaf(gb.y, accA[3] + accB[3], -gb.x), y[3]);
             }
         }
+        yy[0] = fmaf(s0, fmaf(ga.y, accA[0] + accB[0], -ga.x), yy[0]);
+        yy[1] = fmaf(s0, fmaf(gb.y, accA[1] + accB[1], -gb.x), yy[1]);
+        yy[2] = fmaf(s1, fmaf(ga.y, accA[2] + accB[2], -ga.x), yy[2]);
+        yy[3] = fmaf(s1, fmaf(gb.y, accA[3] + accB[3], -gb.x), yy[3]);
+    };
+
+    float y[4] = {0.f, 0.f, 0.f, 0.f};
+    int stage = 0;
+    bool first = true;
+    for (;;) {
+        cp_async_wait<kStages - 1>();           // all but the newest three groups are done: this slot has landed
+        __syncwarp();
+        const uint4 mt = lds128(meta_u32 + stage * 16);          // tile, chunk, slot, last-of-run
+        if ((int)mt.x < 0) break;
+        if (first) { QTRACE(3); first = false; }
+        const int ch = (int)mt.y;
+        const uint32_t rowa = lane_row_u32 + stage * GE::STAGE_BYTES, rowb = rowa + 8 * GE::PITCH;
+        const uint32_t sca = lane_sc_u32 + stage * GE::STAGE_BYTES, scb = sca + 8 * 16;
+        __align__(16) __half sc0[8], sc1[8];
+        if constexpr (GE::CG == 8) {
+            *reinterpret_cast<uint4*>(sc0) = lds128(sca); *reinterpret_cast<uint4*>(sc1) = lds128(scb);
+        } else if constexpr (GE::CG == 4) {
+            *reinterpret_cast<uint2*>(sc0) = lds64(sca); *reinterpret_cast<uint2*>(sc1) = lds64(scb);
+        } else {
+            *reinterpret_cast<uint32_t*>(sc0) = lds32(sca); *reinterpret_cast<uint32_t*>(sc1) = lds32(scb);
+        }
+        const int G0 = ch * GE::CG;
+        if (G0 + GE::CG <= ng_total) {             // full chunk: straight-line code
+#pragma unroll
+            for (int gi = 0; gi < GE::CG; ++gi)
+                do_group(rowa, rowb, gi, G0 + gi, __half2float(sc0[gi]), __half2float(sc1[gi]), y);
+        } else {                                   // last, shorter chunk of a row
+#pragma unroll
+            for (int gi = 0; gi < GE::CG; ++gi)
+                if (G0 + gi < ng_total)
+                    do_group(rowa, rowb, gi, G0 + gi, __half2float(sc0[gi]), __half2float(sc1[gi]), y);
+        }
         if (mt.w) {                                   // run complete: park its partial sums
-            if (t < TT) *reinterpret_cast<float4*>(slots + (size_t)mt.z * SLOT_BYTES + (g * TT + t) * 16) =
-                            make_float4(y[0], y[1], y[2], y[3]);
+            if (t < TT) sts128f(slots_u32 + mt.z * SLOT_BYTES, make_float4(y[0], y[1], y[2], y[3]));
             y[0] = y[1] = y[2] = y[3] = 0.f;
         }
         __syncwarp();                               // every lane is done reading the slot before it is refilled
-        --ahead;
-        stage = stage + 1 == p.stages ? 0 : stage + 1;
+        issue_next(stage);
+        stage = (stage + 1) & (kStages - 1);
     }
     cp_async_wait<0>();
     QTRACE(4);
@@ -820,16 +863,11 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     // per warp: 4 ring descriptors (64 B) + the epilogue prefetch buffer + the ring itself
     const int epi_bytes = align_up(kTileRows * (pl.ocb + pl.rb) + 32, 16);
     const int avail = kMaxDynSmem - off;
-    int nw = 0, stages = 0;
-    for (int want = 3; want >= 2 && !nw; --want)
-        for (int cand = 16; cand >= 4; cand -= 4) {
-            const int fixed = cand * (64 + epi_bytes);
-            if (avail > fixed && (avail - fixed) / (cand * stage_bytes) >= want) {
-                nw = cand; stages = (avail - fixed) / (cand * stage_bytes); break;
-            }
-        }
+    int nw = 0;
+    const int stages = kStages;
+    for (int cand = kMaxWarps; cand >= 4 && !nw; cand -= 4)
+        if (avail >= cand * (64 + epi_bytes + stages * stage_bytes)) nw = cand;
     if (!nw) return pl;
-    if (stages > 4) stages = 4;
     pl.nw = nw; pl.stages = stages;
     pl.off_meta = off;  off += nw * 64;
     pl.off_epi = off;   off = align_up(off + nw * epi_bytes, 128);
