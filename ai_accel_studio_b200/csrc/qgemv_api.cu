@@ -61,7 +61,7 @@ int validate(const qgemv_problem* p, size_t need) {
     return QGEMV_OK;
 }
 
-Args make_args(const qgemv_problem& p) {
+Args make_args(const qgemv_problem& p, size_t partial_floats) {
     Args a{};
     a.x = p.x; a.ldx = p.ldx;
     a.packed = p.packed; a.ldp = p.ldp;
@@ -76,6 +76,7 @@ Args make_args(const qgemv_problem& p) {
     a.t = reinterpret_cast<float*>(ws + kWsTOff);
     a.counters = reinterpret_cast<int*>(ws + kWsCounterOff);
     a.partial = reinterpret_cast<float*>(ws + kWsPartialOff);
+    a.tparts = a.partial + (partial_floats - 8 * QGEMV_MAX_M * kMaxRank);
     a.m = p.m; a.n = p.n; a.kpad = p.k_padded; a.korig = p.k_original; a.group = p.group;
     a.act = p.act; a.oc = p.outliers; a.rank = p.rank;
     a.splits = 1; a.kspan = p.k_padded;
@@ -118,7 +119,7 @@ int run_checked(const qgemv_problem* p, void* stream, size_t need_bytes, size_t 
     const int v = validate(p, need_bytes);
     if (v != QGEMV_OK) return v;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    Args a = make_args(*p);
+    Args a = make_args(*p, partial_floats);
     const bool bf16 = p->x_dtype == QGEMV_BF16;
 
     MmaPlan plan{};
@@ -133,7 +134,7 @@ int run_checked(const qgemv_problem* p, void* stream, size_t need_bytes, size_t 
             return QGEMV_ERR_SHAPE;
         }
     }
-    if (a.rank > 0) {
+    if (a.rank > 0 && !(use_mma && plan.t_inline)) {
         const int r = launch_residual_t(a, bf16, s);
         if (r != QGEMV_OK) return r;
     }

@@ -36,6 +36,7 @@ struct Args {
     float* t;                 // residual projections (workspace)
     int* counters;            // split-K counters (workspace)
     float* partial;           // split-K partials (workspace)
+    float* tparts;            // per-K-part residual projections (tail of the partial area)
     int m, n, kpad, korig, group, act, oc, rank;
     int splits;               // number of K splits (grid.y)
     int kspan;                // codes per K split (multiple of the group)
@@ -76,6 +77,8 @@ struct MmaPlan {
     int nt, nch, ng;        // 16-row tiles, chunks per tile, groups per row
     int rlen, rpt;          // chunks per run, runs per tile
     int tile_aligned;       // CTAs own whole tiles
+    int t_inline, t_parts;  // residual projections computed inside the fused kernel; K parts for that
+    int off_tt;
     int scales_async, epi_async, ocb, rb, epi_bytes;
     int smem_bytes;         // dynamic shared memory
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;

@@ -46,6 +46,8 @@ namespace {
 constexpr int kMaxWarps = QGEMV_MAX_WARPS;   // warps per CTA the kernel is compiled for (register budget = 65536 / (32 * warps))
 constexpr int kTileRows = 16;          // weight rows per mma tile (one warp owns one tile at a time)
 constexpr int kMaxOutliers = 256;      // outlier activations staged in shared memory
+constexpr int kMaxTParts = 8;
+constexpr int kTPartFloats = kMaxTParts * QGEMV_MAX_M * kMaxRank;   // tail of the partial-sum scratch
 
 struct MmaArgs {
     Args a;
@@ -64,6 +66,9 @@ struct MmaArgs {
     int epi_bytes;     // bytes of one warp's epilogue prefetch buffer
     int wait_for_x;    // 1: the producer of x may still be running when this kernel starts
     int tile_aligned;  // 1: every CTA owns whole tiles
+    int t_inline;      // 1: the residual projections t = V.x are computed by the first CTAs of this kernel
+    int t_parts;       // K is cut into this many parts of 8 * blockDim.x columns for that
+    int off_tt;        // shared-memory table of t
     // dynamic shared memory layout (byte offsets)
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
 };
@@ -127,6 +132,11 @@ __device__ __forceinline__ void sts128f(uint32_t a, float4 v) {
 // block until the kernels this one depends on have completed and flushed their writes.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ int ld_acquire_s32(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -229,10 +239,50 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
     int col0 = -1;
     if (tid < n_xo) col0 = a.oidx[tid / M];
     load_items(0);
+    // Residual projections t[m][c] = sum_k V[c,k] x[m,k], computed in-kernel: job j = (column c,
+    // K-part) belongs to CTA j (there are never more jobs than CTAs).  Its loads are issued here,
+    // with the activation loads, ahead of the weight prefetch.
+    const int t_jobs = p.t_inline ? a.rank * p.t_parts : 0;
+    const bool has_job = (int)blockIdx.x < t_jobs;
+    const int t_part_k = nthr * 8;                 // columns of V one job covers: one 16-byte piece per thread
+    uint4 tv = make_uint4(0u, 0u, 0u, 0u), tx[M];
+    int* t_cnt = reinterpret_cast<int*>(smem + 16);
+    if (tid == 0) { *t_cnt = 0; *reinterpret_cast<int*>(smem + 20) = 0; }
+    if (has_job) {
+        const int c = blockIdx.x % a.rank, part = blockIdx.x / a.rank;
+        const int k = part * t_part_k + tid * 8;
+        const bool live = k < a.korig;
+        if (live) tv = *reinterpret_cast<const uint4*>(a.rv + (size_t)c * a.ldv + k);
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+            tx[m] = live ? *reinterpret_cast<const uint4*>(x + (size_t)m * a.ldx + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
     // Every warp's activation loads are queued before any warp starts the bulk weight prefetch
     // (the barrier waits for the issue of the loads, not for their data).
     __syncthreads();
     after_loads();
+    if (has_job) {
+        // every warp reduces its 256 columns and hands the M partial sums to warp 0 (see the kernel)
+        const int warp_id = tid >> 5, lane_id = tid & 31;
+        float ts[M];
+        const __half* vh = reinterpret_cast<const __half*>(&tv);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const XT* xh = reinterpret_cast<const XT*>(&tx[m]);
+            ts[m] = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) ts[m] = fmaf(__half2float(vh[q]), Act16<BF16>::to_float(xh[q]), ts[m]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ts[m] += __shfl_xor_sync(0xffffffffu, ts[m], o);
+        }
+        volatile float* red = reinterpret_cast<volatile float*>(smem + p.off_tt);   // scratch until the table is built
+        if (lane_id == 0) {
+#pragma unroll
+            for (int m = 0; m < M; ++m) red[warp_id * M + m] = ts[m];
+            __threadfence_block();
+            atomicAdd(t_cnt, 1);
+        }
+    }
 
     for (int base = 0; base < items; base += span) {
         if (base) load_items(base);
@@ -360,7 +410,7 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
         const unsigned char* preu = pre ? pre + kTileRows * p.ocb : nullptr;
         const __half* ru0 = pre ? reinterpret_cast<const __half*>(preu + g * p.rb) : a.ru + (size_t)c0 * a.ldu;
         const __half* ru1 = pre ? reinterpret_cast<const __half*>(preu + (g + 8) * p.rb) : a.ru + (size_t)c1 * a.ldu;
-        if (a.rank > 0) pdl_wait();            // the residual projections come from the kernel launched just before
+        const float* tt = reinterpret_cast<const float*>(smem + p.off_tt);
         for (int qb = 0; qb < a.rank; qb += 4 * JB) {
             __half w0[JB], w1[JB];
             float tq[JB][M];
@@ -371,7 +421,7 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
                 w1[i] = q < a.rank ? ru1[q] : __half(0.0f);
                 const int qc = min(q, a.rank - 1);
 #pragma unroll
-                for (int m = 0; m < M; ++m) tq[i][m] = ld_cg_f32(a.t + m * kMaxRank + qc);
+                for (int m = 0; m < M; ++m) tq[i][m] = tt[qc * M + m];
             }
 #pragma unroll
             for (int i = 0; i < JB; ++i) {
@@ -452,8 +502,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     constexpr int PPR = GE::CB / 16;                 // 16-byte pieces per row of a full chunk
     constexpr int RPI = 32 / PPR;                    // rows covered by one warp-wide copy instruction
     const int lrow = lane / PPR, lcol = lane % PPR;
-    // Runs are dealt round-robin: warp w takes runs r0 + w, r0 + w + nw, ...
-    int pf_run = r0 + warp, pf_tile = 0, pf_j = 0, pf_ch = 0, pf_end = 0;     // pf_j: run index inside the tile
+    // Runs are dealt round-robin: warp w takes runs r0 + w, r0 + w + nw, ...  In a CTA that also
+    // computes a residual projection (see stage_activations) warp 0 takes no runs: it collects and
+    // publishes that result, which needs a __threadfence() that must not sit behind queued copies.
+    const bool has_job = p.t_inline && (int)blockIdx.x < a.rank * p.t_parts;
+    const int w0 = has_job ? 1 : 0, nwk = p.nw - w0;
+    int pf_run = warp >= w0 ? r0 + warp - w0 : r1, pf_tile = 0, pf_j = 0, pf_ch = 0, pf_end = 0;   // pf_j: run index inside the tile
     if (pf_run < r1) {
         pf_tile = pf_run / p.rpt;
         pf_j = pf_run - pf_tile * p.rpt;
@@ -478,8 +532,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     const bool ragged_n = (a.n % kTileRows) != 0;
     auto issue_next = [&](int s) {
         if (pf_run >= 0 && pf_ch == pf_end) {          // current run exhausted: step to this warp's next run
-            pf_run += p.nw;
-            pf_j += p.nw;
+            pf_run += nwk;
+            pf_j += nwk;
             while (pf_j >= p.rpt) { pf_j -= p.rpt; ++pf_tile; }
             if (pf_run < r1) {
                 pf_ch = pf_j * p.rlen;
@@ -565,6 +619,28 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     for (int s = 1; s < kStages; ++s) issue_next(s);
     __syncthreads();                                  // staged activations visible to every warp
     QTRACE(2);
+    if (has_job && warp == 0) {
+        // Collect the warps' partial sums (they are resident and about to arrive: short bounded
+        // wait), add them in warp order, publish for every CTA's epilogue.
+        volatile int* t_cnt = reinterpret_cast<volatile int*>(smem + 16);
+        volatile float* red = reinterpret_cast<volatile float*>(smem + p.off_tt);
+        if (lane == 0) {
+            int spins = 0;
+            while (*t_cnt < p.nw) {
+                if (++spins > (1 << 22)) { atomicExch(a.counters + (kWsMaxCounters - 1), 1); break; }
+            }
+        }
+        __syncwarp();
+        if (lane < M) {
+            float tot = 0.0f;
+            for (int w = 0; w < p.nw; ++w) tot += red[w * M + lane];
+            const int c = blockIdx.x % a.rank, part = blockIdx.x / a.rank;
+            a.tparts[(part * QGEMV_MAX_M + lane) * kMaxRank + c] = tot;
+            __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0) atomicAdd(a.counters + (kWsMaxCounters - 2), 1);           // one more job published
+    }
 
     const int ma = min(2 * t, M - 1), mb = min(2 * t + 1, M - 1);
     unsigned char* slots = smem + p.off_slots;
@@ -678,7 +754,41 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     }
     cp_async_wait<0>();
     QTRACE(4);
-    __syncthreads();                                  // every run of this CTA is parked
+    // Table of residual projections t[q][m] in shared memory, built by whichever warp leaves its
+    // main loop first, so that the global-memory latency hides behind the warps still computing.
+    if (a.rank > 0) {
+        int* t_builder = reinterpret_cast<int*>(smem + 20);
+        int mine = 0;
+        if (lane == 0) mine = atomicAdd(t_builder, 1) == 0;
+        mine = __shfl_sync(0xffffffffu, mine, 0);
+        if (mine) {
+            float* tt = reinterpret_cast<float*>(smem + p.off_tt);
+            if (p.t_inline) {
+                if (lane == 0) {                      // published long ago in practice; the wait is bounded
+                    const int want = a.rank * p.t_parts;
+                    int spins = 0;
+                    while (ld_acquire_s32(a.counters + (kWsMaxCounters - 2)) < want) {
+                        if (++spins > (1 << 22)) { atomicExch(a.counters + (kWsMaxCounters - 1), 1); break; }
+                        __nanosleep(64);
+                    }
+                }
+                __syncwarp();
+                for (int i = lane; i < a.rank * M; i += 32) {
+                    const int q = i / M, m = i - q * M;
+                    float v = 0.0f;
+                    for (int part = 0; part < p.t_parts; ++part) v += ld_cg_f32(a.tparts + (part * QGEMV_MAX_M + m) * kMaxRank + q);
+                    tt[i] = v;
+                }
+            } else {
+                pdl_wait();                           // t comes from the kernel launched just before this one
+                for (int i = lane; i < a.rank * M; i += 32) {
+                    const int q = i / M, m = i - q * M;
+                    tt[i] = ld_cg_f32(a.t + m * kMaxRank + q);
+                }
+            }
+        }
+    }
+    __syncthreads();                                  // every run of this CTA is parked, the table is complete
 
     // ---- tiles: add the runs in order, finish or hand over --------------------------------------
     for (int tile = T0 + warp; tile <= T1; tile += p.nw) {
@@ -737,6 +847,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         }
     }
     QTRACE(5);
+    if (p.t_inline && a.rank > 0) {
+        // The last CTA to get here puts the two residual counters back to zero for the next launch.
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            const int old = atomicAdd(a.counters + (kWsMaxCounters - 3), 1);
+            if (old == (int)gridDim.x - 1) {
+                a.counters[kWsMaxCounters - 2] = 0;
+                a.counters[kWsMaxCounters - 3] = 0;
+            }
+        }
+    }
 }
 
 constexpr int kMaxDynSmem = 232448;   // 227 KB per CTA on sm_100
@@ -821,7 +943,7 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     pl.ng = p.k_padded / p.group;
     pl.nch = (pl.ng + cg - 1) / cg;
     pl.nt = (p.n + kTileRows - 1) / kTileRows;
-    if (pl.nt > kWsMaxCounters - 1) return pl;
+    if (pl.nt > kWsMaxCounters - 4) return pl;          // the last three counters are status / residual bookkeeping
     if ((long long)pl.nt * pl.nch > 0x3fffffff) return pl;
     const int sms = sm_count();
     // Runs: consecutive chunks of one tile.  One chunk per run unless a CTA would then need more
@@ -845,7 +967,8 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     }
     if (pl.tile_aligned) slot_cap = ((pl.nt + grid - 1) / grid) * rpt;
     if (slot_cap * slot_bytes > 65536) return pl;
-    if ((size_t)grid * 2 * 4 * 32 > partial_floats) return pl;
+    if ((size_t)grid * 2 * 4 * 32 + kTPartFloats > partial_floats) return pl;
+
     pl.scales_async = (p.lds % cg == 0) && al(p.scales, (size_t)cg * 2) ? 1 : 0;
     pl.ocb = align_up(p.outliers * 2, 16);
     pl.rb = align_up(p.rank * 2, 16);
@@ -858,6 +981,7 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     int off = 64;
     pl.off_xo = off;    off = align_up(off + p.outliers * p.m * 4, 16);
     pl.off_gx = off;    off = align_up(off + pl.ng * p.m * 8, 16);
+    pl.off_tt = off;    off = align_up(off + (p.rank * p.m > 64 ? p.rank * p.m : 64) * 4, 16);
     pl.off_slots = off; off = align_up(off + slot_cap * slot_bytes, 128);
     pl.off_xs = off;    off = align_up(off + p.m * p.k_padded * 2, 128);
     // per warp: 4 ring descriptors (64 B) + the epilogue prefetch buffer + the ring itself
@@ -869,6 +993,9 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
         if (avail >= cand * (64 + epi_bytes + stages * stage_bytes)) nw = cand;
     if (!nw) return pl;
     pl.nw = nw; pl.stages = stages;
+    pl.t_parts = (p.k_original + nw * 256 - 1) / (nw * 256);
+    pl.t_inline = (p.rank > 0 && p.k_original % 8 == 0 && p.ldv % 8 == 0 && al(p.res_v, 16) && pl.t_parts <= kMaxTParts &&
+                   p.rank * pl.t_parts <= grid) ? 1 : 0;
     pl.off_meta = off;  off += nw * 64;
     pl.off_epi = off;   off = align_up(off + nw * epi_bytes, 128);
     pl.epi_bytes = epi_bytes;
@@ -892,7 +1019,8 @@ int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, cudaStream
     p.epi_bytes = pl.epi_bytes;
     p.off_xo = pl.off_xo; p.off_gx = pl.off_gx; p.off_slots = pl.off_slots; p.off_epi = pl.off_epi;
     p.off_meta = pl.off_meta; p.off_xs = pl.off_xs; p.off_ring = pl.off_ring;
-    p.wait_for_x = a.rank > 0 ? 0 : 1;
+    p.t_inline = pl.t_inline; p.t_parts = pl.t_parts; p.off_tt = pl.off_tt;
+    p.wait_for_x = (a.rank > 0 && !pl.t_inline) ? 0 : 1;
     p.tile_aligned = pl.tile_aligned;
     return bits == 2 ? launch_gb<2>(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s)
                      : launch_gb<4>(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s);

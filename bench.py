@@ -43,11 +43,18 @@ WORKLOADS = {
                name="int4_gemv_M4_K4096_N11008_g128_oc32_r8"),
     "c1": dict(bits=2, m=1, n=4096, k=4096, group=64, outliers=0, rank=0,
                name="int2_gemv_M1_K4096_N4096_g64"),
+    # variants used to attribute time (not headline workloads)
+    "c2_plain": dict(bits=4, m=4, n=11008, k=4096, group=128, outliers=0, rank=0,
+                     name="int4_gemv_M4_K4096_N11008_g128_plain"),
+    "int2_big": dict(bits=2, m=1, n=14336, k=4096, group=128, outliers=32, rank=8,
+                     name="int2_gemv_M1_K4096_N14336_g128_oc32_r8"),
+    "int2_down": dict(bits=2, m=1, n=4096, k=14336, group=128, outliers=64, rank=8,
+                      name="int2_gemv_M1_K14336_N4096_g128_oc64_r8"),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (None until a capture exists for that workload).
-NCU_TRAFFIC_BYTES = {"c2": None, "c1": None}
+NCU_TRAFFIC_BYTES = {"c2": 24229632, "c1": 4793856}
 
 
 def algorithmic_bytes(w) -> int:
