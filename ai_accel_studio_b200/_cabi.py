@@ -17,7 +17,7 @@ KERNEL = {"auto": 0, "simt": 1, "mma": 2}
 MAX_M = 4
 ABI_VERSION = 1
 
-EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
+EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem")
 
 
@@ -67,6 +67,8 @@ def lib():
     l.qgemv_workspace_bytes.restype = C.c_size_t
     l.qgemv_plan_name.argtypes = [C.POINTER(Problem)]
     l.qgemv_plan_name.restype = C.c_char_p
+    l.qgemv_plan_launches.argtypes = [C.POINTER(Problem)]
+    l.qgemv_plan_launches.restype = C.c_int
     l.qdequant.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
                            C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     l.qdequant.restype = C.c_int
@@ -101,6 +103,13 @@ def workspace_bytes(bits: int, m: int, n: int, k_padded: int, group: int, rank: 
 
 def run(problem: Problem, stream: int) -> None:
     check(lib().qgemv_run(C.byref(problem), C.c_void_p(stream)))
+
+
+def plan_launches(problem: Problem) -> int:
+    r = int(lib().qgemv_plan_launches(C.byref(problem)))
+    if r < 0:
+        raise QgemvError(r, last_error())
+    return r
 
 
 def run_static(problem: Problem, stream: int) -> None:

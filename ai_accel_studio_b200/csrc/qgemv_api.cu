@@ -196,6 +196,18 @@ extern "C" int qgemv_run_static(const qgemv_problem* p, void* stream) {
     return run_checked(&q, stream, kStaticScratchBytes, kStaticPartialFloats);
 }
 
+extern "C" int qgemv_plan_launches(const qgemv_problem* p) {
+    const int v = validate(p, qgemv_workspace_bytes(0, 0, 0, 0, 0, 0));
+    if (v != QGEMV_OK) return v;
+    bool inline_t = false;
+    if (p->kernel != QGEMV_KERNEL_SIMT) {
+        const MmaPlan plan = plan_mma(*p, kMaxPartialFloats);
+        if (!plan.ok && p->kernel == QGEMV_KERNEL_MMA) return QGEMV_ERR_SHAPE;
+        inline_t = plan.ok && plan.t_inline;
+    }
+    return (p->rank > 0 && !inline_t) ? 2 : 1;
+}
+
 extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {
     return run_checked(p, stream, qgemv_workspace_bytes(0, 0, 0, 0, 0, 0), kMaxPartialFloats);
 }

@@ -6,10 +6,10 @@
 // issue bound (qgemv_simt.cu measures that).  Here the per-weight cost is ~0.6 instructions:
 //
 //  * Packed rows are brought into a per-warp shared-memory ring with 16-byte asynchronous copies
-//    (cp.async.cg, 256 contiguous bytes per row per chunk) -- no staging registers, rows padded
-//    so that every later shared-memory read is conflict free, ~100 KB in flight per SM.
-//    (One cp.async.bulk per row per chunk was tried first: the TMA engine needed ~110 cycles
-//    per 128-256 byte request per SM, 8x too slow for this access pattern.)
+//    (cp.async.cg, 128 contiguous bytes per row per chunk, pieces XOR-swizzled so that every later
+//    shared-memory read is conflict free without padding) -- no staging registers, ~100 KB in
+//    flight per SM.  (Filling the ring with one cp.async.bulk per row per chunk through the TMA
+//    engine measured the same; cp.async needs no mbarriers and allows the swizzle.)
 //  * Codes are NOT converted to numbers.  A 32-bit word is AND-ed with a mask that leaves one
 //    code in the low mantissa bits of each 16-bit half; read as fp16 that is the subnormal
 //    value code * radix^c * 2^-24 (radix = 4 for INT2, 16 for INT4, c = position class).  The
@@ -31,7 +31,9 @@
 //    group scales sit in the ring beside their chunk, the outlier / residual rows of a warp's
 //    first tile are prefetched at kernel start.  A plain load issued while ~100 KB per SM of
 //    prefetch is queued would wait behind all of it.
-//  * Epilogue in the same kernel: exact fp16 outlier columns, rank-r residual, bias, activation.
+//  * Epilogue in the same kernel: exact fp16 outlier columns, rank-r residual (its projections
+//    t = V.x are computed by the first CTAs of the same launch and published through global
+//    memory), bias, activation.
 //
 // Replaces _decode_gemv (ai_accel_lab/kernels/decode_int2.py:43-96) and _decode_int4_gemv
 // (ai_accel_lab/kernels/groupwise_int4.py:85-107) of the reference project.

@@ -169,3 +169,13 @@ def plan_name(x, packed, scales, bits, group, k_original, outliers=0, rank=0, ke
     p = _problem(x, packed, scales, None, None, None, None, None, y, ws, bits, group, k_original, 0,
                  _cabi.KERNEL[kernel])
     return _cabi.plan_name(p)
+
+
+def plan_launches(x, packed, scales, bits, group, k_original, outlier_idx=None, outlier_weight=None,
+                  res_u=None, res_v=None, kernel="auto") -> int:
+    """Number of kernel launches one call with these operands issues (no launch happens)."""
+    ws = ensure_workspace(x.device)
+    y = torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device=x.device)
+    p = _problem(x, packed, scales, None, outlier_idx, outlier_weight, res_u, res_v, y, ws, bits, group,
+                 k_original, 0, _cabi.KERNEL[kernel])
+    return _cabi.plan_launches(p)

@@ -280,7 +280,9 @@ def run_gpu_arm(args, w):
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         outs = [gemv(i, xs_dev[i]) for i in range(RING)]
-    launches_per_gemv = 2 if w["rank"] else 1
+    s0 = sets[0]
+    launches_per_gemv = ops.plan_launches(xs_dev[0], s0["packed"], s0["scales"], bits, w["group"], k, s0.get("outlier_idx"),
+                                          s0.get("outlier_weight"), s0.get("res_u"), s0.get("res_v"), kernel=args.kernel)
 
     def barrier():
         if world > 1:
@@ -367,8 +369,8 @@ def run_gpu_arm(args, w):
             roofline=dict(bound="hbm", achieved=per_gpu, peak=peak, unit="GB/s", frac=per_gpu / peak,
                           traffic=NCU_TRAFFIC_BYTES.get(args.workload), peak_source=f"{peak_kind} copy bandwidth",
                           algorithmic_bytes_per_launch=ab,
-                          note="launch duration = event time of the timed region / GEMVs (includes the small "
-                               "residual-projection kernel and inter-kernel gaps)"),
+                          note="launch duration = event time of the timed region / GEMVs (includes inter-kernel gaps; "
+                               f"{launches_per_gemv} launch(es) per GEMV)"),
             clocks=clocks,
         )
         if world == 1 and not args.no_cpu:

@@ -117,6 +117,11 @@ size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, int group, in
  * NULL if the problem is invalid.  No launch happens. */
 const char* qgemv_plan_name(const qgemv_problem* p);
 
+/* Number of kernel launches qgemv_run would issue for `p` (1 or 2: the general kernel and a few
+ * shapes of the fast one compute the residual projections in a small kernel of their own), or a
+ * negative QGEMV_ERR_* if the problem is invalid.  No launch happens. */
+int qgemv_plan_launches(const qgemv_problem* p);
+
 /* Dequantise to a dense [N, Korig] matrix of out_dtype (QGEMV_F16 / BF16 / F32), bit-identical to
  * the reference's torch expression `levels.to(dtype)[codes] * scales.to(dtype)[:, k // group]`.
  * Replaces: unpack_groupwise_int2  ai_accel_lab/kernels/groupwise_int2.py:122-130,
