@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--probs", type=float, nargs=3, default=(0.6, 0.3, 0.1), help="P(INT2) P(INT4) P(FP16)")
     ap.add_argument("--variants", nargs="+", default=["mixed", "fp16"], choices=["mixed", "fp16"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--compile-layers", action="store_true",
+                    help="fuse the non-GEMV work of each decoder layer with torch.compile (regional compilation)")
     a = ap.parse_args()
 
     import torch.distributed as dist
@@ -43,7 +45,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     for variant in a.variants:
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
-                                  a.layers, use_cuda_graph=not a.no_graph)
+                                  a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers)
         if world > 1:
             t = torch.tensor([res["decode_tokens_s"]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)          # the slowest rank sets the pace
@@ -55,7 +57,8 @@ def main():
                         ttft_ms=res["ttft_ms"], weight_bytes_per_rank=res["total"], packed_bytes=res["packed_bytes"],
                         fp16_bytes=res["fp16_bytes"],
                         weight_GBps_per_gpu=res["total"] * tps / a.batch / 1e9,
-                        peak_vram_gb=res.get("peak_vram_gb"), cuda_graph=not a.no_graph)
+                        peak_vram_gb=res.get("peak_vram_gb"), cuda_graph=not a.no_graph,
+                        compiled_layers=a.compile_layers)
             print(json.dumps(line), flush=True)
         del res
         gc.collect()

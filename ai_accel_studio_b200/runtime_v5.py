@@ -39,6 +39,21 @@ def prepare_static_compile(model, fullgraph=False):
     return model, status
 
 
+def compile_decoder_layers(model):
+    """Fuse the element-wise work between the packed GEMVs (norms, rotary embedding, SwiGLU, residual
+    adds) by compiling each decoder layer with Inductor -- regional compilation: all layers share one
+    compiled artefact.  CUDA graphs stay explicit (StaticGraphDecoder.capture); the packed ops are
+    opaque custom ops to the compiler."""
+    layers = getattr(getattr(model, "model", model), "layers", None)
+    if layers is None:
+        raise ValueError("model has no .model.layers to compile")
+    for layer in layers:
+        if not getattr(layer, "_b200q_compiled", False):
+            layer.forward = torch.compile(layer.forward, dynamic=False)
+            layer._b200q_compiled = True
+    return model
+
+
 def _cuda_event_ms(fn):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
@@ -56,9 +71,11 @@ class StaticGraphDecoder:
     synchronisation in between and returns the ``[B, n]`` tokens.
     """
 
-    def __init__(self, model, batch_size: int, max_cache_len: int, device=None, dtype=None):
+    def __init__(self, model, batch_size: int, max_cache_len: int, device=None, dtype=None, compile_layers=False):
         from transformers import StaticCache
         self.model = model
+        if compile_layers:
+            compile_decoder_layers(model)
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         self.batch = int(batch_size)
         self.max_len = int(max_cache_len)
@@ -129,7 +146,7 @@ class StaticGraphDecoder:
 
 @torch.no_grad()
 def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens=64, device="cuda", warmups=2,
-                              input_ids=None, use_cuda_graph=True):
+                              input_ids=None, use_cuda_graph=True, compile_layers=False):
     """Fixed-length greedy generation benchmark (reference protocol, ai_accel_lab/runtime_v5.py:29-73).
 
     Either ``tokenizer`` + ``prompt`` (left-padded to a multiple of 8, as the reference does) or
@@ -148,7 +165,7 @@ def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens
     input_ids = input_ids.to(device)
     b, n = input_ids.shape
     cuda = torch.device(device).type == "cuda"
-    dec = StaticGraphDecoder(model, b, n + int(max_new_tokens) + 8, device=device)
+    dec = StaticGraphDecoder(model, b, n + int(max_new_tokens) + 8, device=device, compile_layers=compile_layers)
 
     for _ in range(max(1, int(warmups))):
         dec.prefill(input_ids)

@@ -107,3 +107,17 @@ def test_torch_compile_traces_without_graph_break():
     x = torch.randn(2, 512).half().cuda()
     fn = torch.compile(lambda t: torch.relu(mod(t)) * 2, fullgraph=True)
     assert torch.equal(fn(x), torch.relu(mod(x)) * 2)
+
+
+def test_kernel_suite_rows_and_speed_gate():
+    from ai_accel_studio_b200.kernel_suite import run_kernel_suite
+    from ai_accel_studio_b200.optimize.planner_v5 import runtime_speedups
+    rows = run_kernel_suite(m=1, n=512, k=1024, group_size=64, repeats=5)
+    assert [r["method"] for r in rows] == ["torch-fp16", "decode-int2-v4", "decode-int4-v5"]
+    assert rows[0]["nmse_vs_dense"] < 1e-6
+    assert rows[2]["cosine_vs_dense"] > 0.99 and rows[1]["cosine_vs_dense"] > 0.85
+    assert all(r["latency_ms"] > 0 and r["speedup"] > 0 for r in rows)
+    lin = nn.Linear(1024, 512).cuda().half()
+    cand = HybridInt4Linear(lin, 128, None, 8).cuda()
+    d, p_, proj = runtime_speedups(lin, cand, torch.randn(32, 1024, device="cuda", dtype=torch.float16))
+    assert d > 0 and p_ > 0 and proj > 0
