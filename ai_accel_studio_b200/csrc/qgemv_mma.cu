@@ -94,8 +94,6 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
-// Ring depth per warp is a compile-time constant so that the wait depth is an immediate.
-constexpr int kStages = 4;
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -170,8 +168,9 @@ struct Geo {
     static constexpr int G = GB * CPB;                   // group size in codes
     static constexpr int TB = GB / 4;                    // bytes one lane reads per row per group
     static constexpr int TW = TB / 4;                    // ... in 32-bit words
-    static constexpr int CB = 128;                       // chunk bytes per row: one 128-byte line
-    static constexpr int CG = CB / GB;                   // groups per chunk (8, 4 or 2)
+    static constexpr int CB = GB == 16 ? 128 : 256;      // chunk bytes per row: one or two 128-byte lines
+    static constexpr int CG = CB / GB;                   // groups per chunk (8 or 4)
+    static constexpr int STAGES = CB == 128 ? 4 : 2;     // ring slots per warp (about 9 KB of ring per warp either way)
     static constexpr int PITCH = CB;                     // rows are dense in shared memory ...
     // ... and bank conflicts are avoided by storing 16-byte piece c of row r at piece position
     // c ^ swz(r): the rows a shared-memory instruction touches together (2 for 16-byte reads,
@@ -494,7 +493,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     const int r1 = p.tile_aligned ? first_unit(cta + 1, p.nt, grid) * p.rpt : first_unit(cta + 1, p.runs, grid);
     const int T0 = r0 / p.rpt, T1 = (r1 - 1) / p.rpt;
 
-    unsigned char* ring = smem + p.off_ring + (size_t)warp * kStages * GE::STAGE_BYTES;
+    unsigned char* ring = smem + p.off_ring + (size_t)warp * GE::STAGES * GE::STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring);
     int4* meta = reinterpret_cast<int4*>(smem + p.off_meta) + warp * 4;      // per stage: tile, chunk, slot, last
     unsigned char* epi = smem + p.off_epi + (size_t)warp * p.epi_bytes;
@@ -618,7 +617,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         issue_next(0);                                // the rest of the ring is filled while computing: a warp that
         QTRACE(1);                                    // queued it all here would sit behind its own copies
     });
-    for (int s = 1; s < kStages; ++s) issue_next(s);
+    for (int s = 1; s < GE::STAGES; ++s) issue_next(s);
     __syncthreads();                                  // staged activations visible to every warp
     QTRACE(2);
     if (has_job && warp == 0) {
@@ -719,7 +718,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     int stage = 0;
     bool first = true;
     for (;;) {
-        cp_async_wait<kStages - 1>();           // all but the newest three groups are done: this slot has landed
+        cp_async_wait<GE::STAGES - 1>();        // all but the newest STAGES-1 groups are done: this slot has landed
         __syncwarp();
         const uint4 mt = lds128(meta_u32 + stage * 16);          // tile, chunk, slot, last-of-run
         if ((int)mt.x < 0) break;
@@ -736,6 +735,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
             *reinterpret_cast<uint32_t*>(sc0) = lds32(sca); *reinterpret_cast<uint32_t*>(sc1) = lds32(scb);
         }
         const int G0 = ch * GE::CG;
+#ifdef QGEMV_NOCOMPUTE                              // measurement aid: stream and bookkeeping only
+        if (G0 < 0)
+#endif
         if (G0 + GE::CG <= ng_total) {             // full chunk: straight-line code
 #pragma unroll
             for (int gi = 0; gi < GE::CG; ++gi)
@@ -752,7 +754,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         }
         __syncwarp();                               // every lane is done reading the slot before it is refilled
         issue_next(stage);
-        stage = (stage + 1) & (kStages - 1);
+        stage = (stage + 1) & (GE::STAGES - 1);
     }
     cp_async_wait<0>();
     QTRACE(4);
@@ -940,7 +942,7 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     auto al = [](const void* q, size_t a) { return reinterpret_cast<uintptr_t>(q) % a == 0; };
     if (!al(p.packed, 16) || p.ldp % 16 || !al(p.x, 16) || p.ldx % 8) return pl;
     if (p.outliers > kMaxOutliers || p.rank > kMaxRank) return pl;
-    const int cb = 128, cg = cb / gb, stage_bytes = kTileRows * cb + kTileRows * 16;
+    const int cb = gb == 16 ? 128 : 256, cg = cb / gb, stage_bytes = kTileRows * cb + kTileRows * 16;
     pl.gb = gb;
     pl.ng = p.k_padded / p.group;
     pl.nch = (pl.ng + cg - 1) / cg;
@@ -990,7 +992,7 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     const int epi_bytes = align_up(kTileRows * (pl.ocb + pl.rb) + 32, 16);
     const int avail = kMaxDynSmem - off;
     int nw = 0;
-    const int stages = kStages;
+    const int stages = cb == 128 ? 4 : 2;
     for (int cand = kMaxWarps; cand >= 4 && !nw; cand -= 4)
         if (avail >= cand * (64 + epi_bytes + stages * stage_bytes)) nw = cand;
     if (!nw) return pl;
