@@ -483,7 +483,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     const Args& a = p.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     pdl_launch_dependents();
-    if (p.wait_for_x) pdl_wait();
 
     // This CTA's share of the runs, and the tiles they touch.
     const int grid = gridDim.x, cta = blockIdx.x;
@@ -590,10 +589,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         cp_async_commit();
     };
 
-    stage_activations<BITS, GB, M, BF16>(p, smem, [&]() {
-        // (runs after the barrier that follows the activation loads; the queue head is visible)
-        QTRACE(7);
-        // Oldest group: the epilogue operands of the tile this warp will finish first.
+    // First copies of this warp: the epilogue operands of the tile it will finish first (oldest
+    // group) and its first ring slot.
+    auto first_prefetch = [&]() {
         const int etile = T0 + warp;
         const bool efull = etile <= T1 && etile * p.rpt >= r0 && (etile + 1) * p.rpt <= r1 &&
                            (etile + 1) * kTileRows <= a.n;
@@ -614,8 +612,20 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
                            reinterpret_cast<const unsigned char*>(a.bias + (size_t)etile * kTileRows) + lane * 16);
         }
         cp_async_commit();
-        issue_next(0);                                // the rest of the ring is filled while computing: a warp that
-        QTRACE(1);                                    // queued it all here would sit behind its own copies
+        issue_next(0);
+    };
+    // The weights do not depend on the previous kernel in the stream, the activations do: when this
+    // kernel was launched early (programmatic dependent launch) the first copies are queued while
+    // it waits for its predecessor; otherwise they are queued right behind the activation loads.
+    const bool early = p.wait_for_x != 0;
+    if (early) {
+        first_prefetch();
+        pdl_wait();
+    }
+    stage_activations<BITS, GB, M, BF16>(p, smem, [&]() {
+        QTRACE(7);
+        if (!early) first_prefetch();
+        QTRACE(1);
     });
     for (int s = 1; s < GE::STAGES; ++s) issue_next(s);
     __syncthreads();                                  // staged activations visible to every warp

@@ -56,6 +56,9 @@ enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_M
  *   outlier_idx int32 [oc] (values < Korig), outlier_w fp16 [N, oc]; oc may be any count >= 0
  *   res_u      fp16 [N, rank], res_v fp16 [rank, Korig]; rank may be 0
  *   y          fp16 or bf16 (same type as x) [M, N]
+ *   The weight-side tensors (packed, scales, bias, outlier_*, res_*) must already be final when
+ *   the call is issued: the kernel may start reading them before the preceding kernel of the
+ *   stream has finished (it waits for that kernel only before it reads x).
  *   workspace  zero-initialised ONCE by the caller, at least qgemv_workspace_bytes() bytes,
  *              256-byte aligned, private to calls that may overlap on the device.  The
  *              kernels leave it ready for the next call (no memset between calls).
