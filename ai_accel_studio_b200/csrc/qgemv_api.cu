@@ -76,7 +76,7 @@ Args make_args(const qgemv_problem& p, size_t partial_floats) {
     a.t = reinterpret_cast<float*>(ws + kWsTOff);
     a.counters = reinterpret_cast<int*>(ws + kWsCounterOff);
     a.partial = reinterpret_cast<float*>(ws + kWsPartialOff);
-    a.tparts = a.partial + (partial_floats - 8 * QGEMV_MAX_M * kMaxRank);
+    a.tparts = a.partial + (partial_floats - kTPartFloats);
     a.m = p.m; a.n = p.n; a.kpad = p.k_padded; a.korig = p.k_original; a.group = p.group;
     a.act = p.act; a.oc = p.outliers; a.rank = p.rank;
     a.splits = 1; a.kspan = p.k_padded;

@@ -18,8 +18,14 @@ namespace qgemv {
 constexpr int    kMaxRank        = 64;
 constexpr size_t kWsTOff         = 0;
 constexpr size_t kWsCounterOff   = 1024;
-constexpr int    kWsMaxCounters  = 16384;          // last entry is the wait-timeout status word
+constexpr int    kWsMaxCounters  = 16384;          // the last four entries are not tile counters:
+constexpr int    kWsStatusIdx    = kWsMaxCounters - 1;   //   wait-timeout status word
+constexpr int    kWsDoneIdx      = kWsMaxCounters - 3;   //   CTAs that finished the current launch
+constexpr int    kWsEpochIdx     = kWsMaxCounters - 4;   //   launches completed so far (tag of in-kernel residual projections)
 constexpr size_t kWsPartialOff   = kWsCounterOff + sizeof(int) * kWsMaxCounters;   // 66560, 256-aligned
+constexpr int    kMaxTParts      = 8;              // K-parts of an in-kernel residual projection
+// tail of the partial-sum area: {fp32 value, launch tag} per (K-part, m, rank column), in 32-bit words
+constexpr int    kTPartFloats    = 2 * kMaxTParts * QGEMV_MAX_M * kMaxRank;
 constexpr size_t kMaxPartialFloats = size_t(1) << 20;                             // 4 MiB of fp32 partial sums
 
 // Device-side view of one problem; a trivially copyable kernel parameter.
@@ -36,7 +42,7 @@ struct Args {
     float* t;                 // residual projections (workspace)
     int* counters;            // split-K counters (workspace)
     float* partial;           // split-K partials (workspace)
-    float* tparts;            // per-K-part residual projections (tail of the partial area)
+    float* tparts;            // per-K-part residual projections, 8-byte {value, tag} words (tail of the partial area)
     int m, n, kpad, korig, group, act, oc, rank;
     int splits;               // number of K splits (grid.y)
     int kspan;                // codes per K split (multiple of the group)

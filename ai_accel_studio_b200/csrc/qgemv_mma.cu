@@ -48,8 +48,6 @@ namespace {
 constexpr int kMaxWarps = QGEMV_MAX_WARPS;   // warps per CTA the kernel is compiled for (register budget = 65536 / (32 * warps))
 constexpr int kTileRows = 16;          // weight rows per mma tile (one warp owns one tile at a time)
 constexpr int kMaxOutliers = 256;      // outlier activations staged in shared memory
-constexpr int kMaxTParts = 8;
-constexpr int kTPartFloats = kMaxTParts * QGEMV_MAX_M * kMaxRank;   // tail of the partial-sum scratch
 
 struct MmaArgs {
     Args a;
@@ -128,15 +126,21 @@ __device__ __forceinline__ float4 lds128f(uint32_t a) {
 __device__ __forceinline__ void sts128f(uint32_t a, float4 v) {
     asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// 64-bit relaxed device-scope accesses: a residual projection travels between CTAs as one aligned
+// {value, launch tag} word, so the value needs no separate flag, fence or counter.
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long v; asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ unsigned ld_relaxed_u32(const int* p) {
+    unsigned v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
 // Programmatic dependent launch: let the next kernel in the stream begin its prologue now, and
 // block until the kernels this one depends on have completed and flushed their writes.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ int ld_acquire_s32(const int* p) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -152,7 +156,7 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
             unsigned long long t_;                                                              \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
             reinterpret_cast<unsigned long long*>(p.a.partial + (kMaxPartialFloats / 2))        \
-                [((size_t)blockIdx.x * 16 + (threadIdx.x >> 5)) * 8 + (slot)] = t_;             \
+                [((size_t)blockIdx.x * 16 + (threadIdx.x >> 5)) * 16 + (slot)] = t_;            \
         }                                                                                       \
     } while (0)
 #else
@@ -239,7 +243,9 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
     const int n_xo = a.oc * M;
     int col0 = -1;
     if (tid < n_xo) col0 = a.oidx[tid / M];
+    QTRACE(10);
     load_items(0);
+    QTRACE(11);
     // Residual projections t[m][c] = sum_k V[c,k] x[m,k], computed in-kernel: job j = (column c,
     // K-part) belongs to CTA j (there are never more jobs than CTAs).  Its loads are issued here,
     // with the activation loads, ahead of the weight prefetch.
@@ -247,8 +253,6 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
     const bool has_job = (int)blockIdx.x < t_jobs;
     const int t_part_k = nthr * 8;                 // columns of V one job covers: one 16-byte piece per thread
     uint4 tv = make_uint4(0u, 0u, 0u, 0u), tx[M];
-    int* t_cnt = reinterpret_cast<int*>(smem + 16);
-    if (tid == 0) { *t_cnt = 0; *reinterpret_cast<int*>(smem + 20) = 0; }
     if (has_job) {
         const int c = blockIdx.x % a.rank, part = blockIdx.x / a.rank;
         const int k = part * t_part_k + tid * 8;
@@ -276,12 +280,10 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ts[m] += __shfl_xor_sync(0xffffffffu, ts[m], o);
         }
-        volatile float* red = reinterpret_cast<volatile float*>(smem + p.off_tt);   // scratch until the table is built
+        float* red = reinterpret_cast<float*>(smem + p.off_tt);   // scratch until the table is built; read after the next barrier
         if (lane_id == 0) {
 #pragma unroll
             for (int m = 0; m < M; ++m) red[warp_id * M + m] = ts[m];
-            __threadfence_block();
-            atomicAdd(t_cnt, 1);
         }
     }
 
@@ -375,6 +377,90 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
 // `pre` points at this warp's prefetched copy of the tile's outlier-weight rows, residual rows
 // and bias (shared memory), or is null, in which case they are read from global memory.
 // ---------------------------------------------------------------------------------------------
+// e0[m] += sum_j w0[j] * v[j][m] (same for e1 with w1) over the columns j = t, t+4, ... < cols that
+// this lane of the quad owns; v is a shared-memory table [cols][M].  JB columns are loaded before
+// they are used.
+template <int M, int JB>
+__device__ __forceinline__ void epi_dot(const __half* w0, const __half* w1, const float* v, int cols, int t,
+                                        float (&e0)[M], float (&e1)[M]) {
+    for (int jb = 0; jb < cols; jb += 4 * JB) {
+        __half h0[JB], h1[JB];
+        float vv[JB][M];
+#pragma unroll
+        for (int i = 0; i < JB; ++i) {
+            const int j = jb + 4 * i + t;
+            const int jc = min(j, cols - 1);
+            h0[i] = j < cols ? w0[j] : __half(0.0f);
+            h1[i] = j < cols ? w1[j] : __half(0.0f);
+            if constexpr (M == 4) {
+                const float4 q = *reinterpret_cast<const float4*>(v + jc * 4);
+                vv[i][0] = q.x; vv[i][1] = q.y; vv[i][2] = q.z; vv[i][3] = q.w;
+            } else if constexpr (M == 2) {
+                const float2 q = *reinterpret_cast<const float2*>(v + jc * 2);
+                vv[i][0] = q.x; vv[i][1] = q.y;
+            } else {
+#pragma unroll
+                for (int m = 0; m < M; ++m) vv[i][m] = v[jc * M + m];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < JB; ++i) {
+            const float f0 = __half2float(h0[i]), f1 = __half2float(h1[i]);
+#pragma unroll
+            for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, vv[i][m], e0[m]); e1[m] = fmaf(f1, vv[i][m], e1[m]); }
+        }
+    }
+}
+template <int M>
+__device__ __forceinline__ void epi_dot_any(const __half* w0, const __half* w1, const float* v, int cols, int t,
+                                            float (&e0)[M], float (&e1)[M]) {
+    if (cols <= 8) epi_dot<M, 2>(w0, w1, v, cols, t, e0, e1);
+    else if (cols <= 16) epi_dot<M, 4>(w0, w1, v, cols, t, e0, e1);
+    else epi_dot<M, 8>(w0, w1, v, cols, t, e0, e1);
+}
+// Adds the quad's column sums and leaves in y the entries this lane owns (rows g / g+8, activation
+// rows 2t and 2t+1).
+template <int M>
+__device__ __forceinline__ void epi_fold(float (&e0)[M], float (&e1)[M], int t, float (&y)[4]) {
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        e0[m] += __shfl_xor_sync(0xffffffffu, e0[m], 1); e0[m] += __shfl_xor_sync(0xffffffffu, e0[m], 2);
+        e1[m] += __shfl_xor_sync(0xffffffffu, e1[m], 1); e1[m] += __shfl_xor_sync(0xffffffffu, e1[m], 2);
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        if (m == 2 * t)     { y[0] += e0[m]; y[2] += e1[m]; }
+        if (m == 2 * t + 1) { y[1] += e0[m]; y[3] += e1[m]; }
+    }
+}
+
+// Outlier-column and residual terms of one tile for this lane's four outputs.  Kept out of line:
+// a launch starts with a cold instruction cache, and problems without these terms should not
+// have to step over their code.
+template <int M>
+__device__ __noinline__ float4 tile_extras(const MmaArgs& p, const unsigned char* smem, int tile, const unsigned char* pre) {
+    const Args& a = p.a;
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int c0 = min(tile * kTileRows + g, a.n - 1), c1 = min(tile * kTileRows + g + 8, a.n - 1);
+    float e0[M], e1[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) { e0[m] = 0.0f; e1[m] = 0.0f; }
+    if (a.oc > 0) {
+        const __half* ow0 = pre ? reinterpret_cast<const __half*>(pre + g * p.ocb) : a.ow + (size_t)c0 * a.ldow;
+        const __half* ow1 = pre ? reinterpret_cast<const __half*>(pre + (g + 8) * p.ocb) : a.ow + (size_t)c1 * a.ldow;
+        epi_dot_any<M>(ow0, ow1, reinterpret_cast<const float*>(smem + p.off_xo), a.oc, t, e0, e1);
+    }
+    if (a.rank > 0) {
+        const unsigned char* preu = pre ? pre + kTileRows * p.ocb : nullptr;
+        const __half* ru0 = pre ? reinterpret_cast<const __half*>(preu + g * p.rb) : a.ru + (size_t)c0 * a.ldu;
+        const __half* ru1 = pre ? reinterpret_cast<const __half*>(preu + (g + 8) * p.rb) : a.ru + (size_t)c1 * a.ldu;
+        epi_dot_any<M>(ru0, ru1, reinterpret_cast<const float*>(smem + p.off_tt), a.rank, t, e0, e1);
+    }
+    float y[4] = {0.f, 0.f, 0.f, 0.f};
+    epi_fold<M>(e0, e1, t, y);
+    return make_float4(y[0], y[1], y[2], y[3]);
+}
+
 template <int M, bool BF16>
 __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned char* smem, int tile, float (&y)[4],
                                             const unsigned char* pre) {
@@ -384,63 +470,8 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
     const int r0 = tile * kTileRows + g, r1 = r0 + 8;
     const int c0 = min(r0, a.n - 1), c1 = min(r1, a.n - 1);
     if (a.oc > 0 || a.rank > 0) {
-        const float* xo = reinterpret_cast<const float*>(smem + p.off_xo);
-        float e0[M], e1[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) { e0[m] = 0.0f; e1[m] = 0.0f; }
-        // The four lanes of a quad split the columns; all loads of a batch are issued before use.
-        constexpr int JB = 8;
-        const __half* ow0 = pre ? reinterpret_cast<const __half*>(pre + g * p.ocb) : a.ow + (size_t)c0 * a.ldow;
-        const __half* ow1 = pre ? reinterpret_cast<const __half*>(pre + (g + 8) * p.ocb) : a.ow + (size_t)c1 * a.ldow;
-        for (int jb = 0; jb < a.oc; jb += 4 * JB) {
-            __half w0[JB], w1[JB];
-#pragma unroll
-            for (int i = 0; i < JB; ++i) {
-                const int j = jb + 4 * i + t;
-                w0[i] = j < a.oc ? ow0[j] : __half(0.0f);
-                w1[i] = j < a.oc ? ow1[j] : __half(0.0f);
-            }
-#pragma unroll
-            for (int i = 0; i < JB; ++i) {
-                const int j = min(jb + 4 * i + t, a.oc - 1);
-                const float f0 = __half2float(w0[i]), f1 = __half2float(w1[i]);
-#pragma unroll
-                for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, xo[j * M + m], e0[m]); e1[m] = fmaf(f1, xo[j * M + m], e1[m]); }
-            }
-        }
-        const unsigned char* preu = pre ? pre + kTileRows * p.ocb : nullptr;
-        const __half* ru0 = pre ? reinterpret_cast<const __half*>(preu + g * p.rb) : a.ru + (size_t)c0 * a.ldu;
-        const __half* ru1 = pre ? reinterpret_cast<const __half*>(preu + (g + 8) * p.rb) : a.ru + (size_t)c1 * a.ldu;
-        const float* tt = reinterpret_cast<const float*>(smem + p.off_tt);
-        for (int qb = 0; qb < a.rank; qb += 4 * JB) {
-            __half w0[JB], w1[JB];
-            float tq[JB][M];
-#pragma unroll
-            for (int i = 0; i < JB; ++i) {
-                const int q = qb + 4 * i + t;
-                w0[i] = q < a.rank ? ru0[q] : __half(0.0f);
-                w1[i] = q < a.rank ? ru1[q] : __half(0.0f);
-                const int qc = min(q, a.rank - 1);
-#pragma unroll
-                for (int m = 0; m < M; ++m) tq[i][m] = tt[qc * M + m];
-            }
-#pragma unroll
-            for (int i = 0; i < JB; ++i) {
-                const float f0 = __half2float(w0[i]), f1 = __half2float(w1[i]);
-#pragma unroll
-                for (int m = 0; m < M; ++m) { e0[m] = fmaf(f0, tq[i][m], e0[m]); e1[m] = fmaf(f1, tq[i][m], e1[m]); }
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            e0[m] += __shfl_xor_sync(0xffffffffu, e0[m], 1); e0[m] += __shfl_xor_sync(0xffffffffu, e0[m], 2);
-            e1[m] += __shfl_xor_sync(0xffffffffu, e1[m], 1); e1[m] += __shfl_xor_sync(0xffffffffu, e1[m], 2);
-        }
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            if (m == 2 * t)     { y[0] += e0[m]; y[2] += e1[m]; }
-            if (m == 2 * t + 1) { y[1] += e0[m]; y[3] += e1[m]; }
-        }
+        const float4 e = tile_extras<M>(p, smem, tile, pre);
+        y[0] += e.x; y[1] += e.y; y[2] += e.z; y[3] += e.w;
     }
     XT* out = static_cast<XT*>(a.y);
     float b0 = 0.0f, b1 = 0.0f;
@@ -469,6 +500,117 @@ __device__ __forceinline__ int first_unit(int w, int units, int parts) {
 }
 __device__ __forceinline__ int owner_of(int u, int units, int parts) {
     return (int)((((unsigned long long)u + 1) * (unsigned)parts - 1) / (unsigned)units);
+}
+
+// Address of entry idx = (part * rank + q) * M + m of the in-kernel residual projections.
+__device__ __forceinline__ const unsigned long long* t_entry(const Args& a, int M, int idx) {
+    const int RM = a.rank * M, part = idx / RM, i = idx - part * RM, q = i / M, m = i - q * M;
+    return reinterpret_cast<const unsigned long long*>(a.tparts) + (part * QGEMV_MAX_M + m) * kMaxRank + q;
+}
+
+// Table of residual projections t[q][m] in shared memory (one warp).  In-kernel projections arrive
+// as {value, launch tag} words from the CTAs that computed them; a small table was requested while
+// the warp was still computing (early0/early1, `requested`), so the trip to L2 is hidden, and a
+// word whose tag is not this launch's is simply read again (bounded).  `scratch` is idle shared
+// memory of the calling warp (64 floats).
+template <int M>
+__device__ __noinline__ void build_t_table(const MmaArgs& p, unsigned char* smem, float* scratch, unsigned t_tag,
+                                           unsigned long long early0, unsigned long long early1, bool requested) {
+    const Args& a = p.a;
+    const int lane = threadIdx.x & 31;
+    float* tt = reinterpret_cast<float*>(smem + p.off_tt);
+    const int RM = a.rank * M;
+    if (!p.t_inline) {
+        pdl_wait();                               // t comes from the kernel launched just before this one
+        for (int i = lane; i < RM; i += 32) {
+            const int q = i / M, m = i - q * M;
+            tt[i] = ld_cg_f32(a.t + m * kMaxRank + q);
+        }
+        return;
+    }
+    const unsigned long long* src = reinterpret_cast<const unsigned long long*>(a.tparts);
+    auto settle = [&](unsigned long long w, const unsigned long long* addr) {
+        int spins = 0;
+        while ((unsigned)(w >> 32) != t_tag) {
+            if (++spins > (1 << 20)) { atomicExch(a.counters + kWsStatusIdx, 1); break; }
+            __nanosleep(32);
+            w = ld_relaxed_u64(addr);
+        }
+        return __uint_as_float((unsigned)w);
+    };
+    const int entries = p.t_parts * RM;
+    if (entries <= 64) {
+        const unsigned long long early[2] = {early0, early1};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int idx = lane + 32 * e;
+            if (idx < entries) {
+                const unsigned long long* addr = t_entry(a, M, idx);
+                scratch[idx] = settle(requested ? early[e] : ld_relaxed_u64(addr), addr);
+            }
+        }
+        __syncwarp();
+        for (int i = lane; i < RM; i += 32) {
+            float v = 0.0f;
+            for (int part = 0; part < p.t_parts; ++part) v += scratch[part * RM + i];
+            tt[i] = v;
+        }
+    } else {
+        for (int i = lane; i < RM; i += 32) {
+            const int q = i / M, m = i - q * M;
+            float v = 0.0f;
+            for (int part = 0; part < p.t_parts; ++part) {
+                const unsigned long long* addr = src + (part * QGEMV_MAX_M + m) * kMaxRank + q;
+                v += settle(ld_relaxed_u64(addr), addr);
+            }
+            tt[i] = v;
+        }
+    }
+}
+
+// A tile whose runs are split between neighbouring CTAs: this CTA parks its sum in global memory
+// and counts its arrival; the last CTA to arrive adds the contributions in CTA order and finishes
+// the tile.  Out of line: tile-aligned launches never come here.
+template <int M, bool BF16>
+__device__ __noinline__ void shared_tile(const MmaArgs& p, const unsigned char* smem, int tile, float4 sum, int slot) {
+    const Args& a = p.a;
+    const int lane = threadIdx.x & 31, grid = gridDim.x, cta = blockIdx.x;
+    float y[4] = {sum.x, sum.y, sum.z, sum.w};
+    float* mine = a.partial + ((size_t)(cta * 2 + slot) * 4) * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mine[i * 32 + lane] = y[i];
+    __threadfence();
+    __syncwarp();
+    const int cf = owner_of(tile * p.rpt, p.runs, grid);
+    const int cl = owner_of(tile * p.rpt + p.rpt - 1, p.runs, grid);
+    int last = 0;
+    if (lane == 0) {
+        const int old = atomicAdd(&a.counters[tile], 1);
+        last = old == cl - cf;
+        if (last) a.counters[tile] = 0;          // ready for the next launch
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    y[0] = y[1] = y[2] = y[3] = 0.f;
+    for (int cb = cf; cb <= cl; cb += 4) {     // four contributors' loads in flight at a time
+        float v[4][4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = min(cb + k, cl);
+            const int sl = tile == first_unit(c, p.runs, grid) / p.rpt ? 0 : 1;
+            const float* src = a.partial + ((size_t)(c * 2 + sl) * 4) * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[k][i] = ld_cg_f32(src + i * 32 + lane);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (cb + k <= cl) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y[i] += v[k][i];
+            }
+    }
+    finish_tile<M, BF16>(p, smem, tile, y, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -502,11 +644,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     constexpr int PPR = GE::CB / 16;                 // 16-byte pieces per row of a full chunk
     constexpr int RPI = 32 / PPR;                    // rows covered by one warp-wide copy instruction
     const int lrow = lane / PPR, lcol = lane % PPR;
-    // Runs are dealt round-robin: warp w takes runs r0 + w, r0 + w + nw, ...  In a CTA that also
-    // computes a residual projection (see stage_activations) warp 0 takes no runs: it collects and
-    // publishes that result, which needs a __threadfence() that must not sit behind queued copies.
-    const bool has_job = p.t_inline && (int)blockIdx.x < a.rank * p.t_parts;
-    const int w0 = has_job ? 1 : 0, nwk = p.nw - w0;
+    // Runs are dealt round-robin: warp w takes runs r0 + w, r0 + w + nw, ...
+    const bool has_job = p.t_inline && (int)blockIdx.x < a.rank * p.t_parts;   // this CTA also computes a residual projection
+    constexpr int w0 = 0;
+    const int nwk = p.nw;
     int pf_run = warp >= w0 ? r0 + warp - w0 : r1, pf_tile = 0, pf_j = 0, pf_ch = 0, pf_end = 0;   // pf_j: run index inside the tile
     if (pf_run < r1) {
         pf_tile = pf_run / p.rpt;
@@ -591,11 +732,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
 
     // First copies of this warp: the epilogue operands of the tile it will finish first (oldest
     // group) and its first ring slot.
+    // Tiles are finished by the warps in reverse order (warp nw-1 takes the CTA's first tile): the
+    // round-robin deal of the runs leaves the high-numbered warps with the fewest runs.
+    const int tw = p.nw - 1 - warp;
+    const int etile = T0 + tw;
+    const bool efull = p.epi_async && etile <= T1 && etile * p.rpt >= r0 && (etile + 1) * p.rpt <= r1 &&
+                       (etile + 1) * kTileRows <= a.n;
     auto first_prefetch = [&]() {
-        const int etile = T0 + warp;
-        const bool efull = etile <= T1 && etile * p.rpt >= r0 && (etile + 1) * p.rpt <= r1 &&
-                           (etile + 1) * kTileRows <= a.n;
-        if (p.epi_async && efull) {
+        if (efull) {
             const int opieces = p.ocb >> 4, upieces = p.rb >> 4;
             for (int i = lane; i < kTileRows * opieces; i += 32) {
                 const int r = i / opieces, c = i - r * opieces;
@@ -614,43 +758,35 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         cp_async_commit();
         issue_next(0);
     };
-    // The weights do not depend on the previous kernel in the stream, the activations do: when this
-    // kernel was launched early (programmatic dependent launch) the first copies are queued while
-    // it waits for its predecessor; otherwise they are queued right behind the activation loads.
-    const bool early = p.wait_for_x != 0;
-    if (early) {
-        first_prefetch();
-        pdl_wait();
-    }
+    // Activations first, weights second: the activation loads are short and everything waits for
+    // them, and loads issued behind the first weight copies are served after those copies.
+    QTRACE(8);
+    if (p.wait_for_x) pdl_wait();
+    QTRACE(9);
+    // Tag of this launch for the residual projections that travel between CTAs (see below): the
+    // workspace holds a launch count that the last CTA of every launch advances.
+    const bool t_reader = p.t_inline && warp == p.nw - 1;
+    unsigned t_tag = 0;
+    if (p.t_inline && (warp == 0 || t_reader)) t_tag = ld_relaxed_u32(a.counters + kWsEpochIdx) + 1u;
     stage_activations<BITS, GB, M, BF16>(p, smem, [&]() {
         QTRACE(7);
-        if (!early) first_prefetch();
+        first_prefetch();
         QTRACE(1);
     });
     for (int s = 1; s < GE::STAGES; ++s) issue_next(s);
     __syncthreads();                                  // staged activations visible to every warp
     QTRACE(2);
     if (has_job && warp == 0) {
-        // Collect the warps' partial sums (they are resident and about to arrive: short bounded
-        // wait), add them in warp order, publish for every CTA's epilogue.
-        volatile int* t_cnt = reinterpret_cast<volatile int*>(smem + 16);
-        volatile float* red = reinterpret_cast<volatile float*>(smem + p.off_tt);
-        if (lane == 0) {
-            int spins = 0;
-            while (*t_cnt < p.nw) {
-                if (++spins > (1 << 22)) { atomicExch(a.counters + (kWsMaxCounters - 1), 1); break; }
-            }
-        }
-        __syncwarp();
+        // The warps' partial sums were written before the barrier above: add them in warp order and
+        // publish {sum, launch tag} for every CTA's epilogue with one relaxed 64-bit store.
+        const float* red = reinterpret_cast<const float*>(smem + p.off_tt);
         if (lane < M) {
             float tot = 0.0f;
             for (int w = 0; w < p.nw; ++w) tot += red[w * M + lane];
             const int c = blockIdx.x % a.rank, part = blockIdx.x / a.rank;
-            a.tparts[(part * QGEMV_MAX_M + lane) * kMaxRank + c] = tot;
-            __threadfence();
+            st_relaxed_u64(reinterpret_cast<unsigned long long*>(a.tparts) + (part * QGEMV_MAX_M + lane) * kMaxRank + c,
+                           ((unsigned long long)t_tag << 32) | __float_as_uint(tot));
         }
-        __syncwarp();
-        if (lane == 0) atomicAdd(a.counters + (kWsMaxCounters - 2), 1);           // one more job published
     }
 
     const int ma = min(2 * t, M - 1), mb = min(2 * t + 1, M - 1);
@@ -724,6 +860,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         yy[3] = fmaf(s1, fmaf(gb.y, accA[3] + accB[3], -gb.x), yy[3]);
     };
 
+    // Residual projections computed by other CTAs: a small table is requested by the reader warp
+    // after its first unit (the producers have published by then) and checked after the loop.
+    const int t_entries = p.t_inline ? p.t_parts * a.rank * M : 0;
+    unsigned long long t_early[2] = {0ull, 0ull};
+    bool t_issued = false;
+    bool t_request = t_reader && t_entries <= 64;
+
     float y[4] = {0.f, 0.f, 0.f, 0.f};
     int stage = 0;
     bool first = true;
@@ -765,48 +908,25 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         __syncwarp();                               // every lane is done reading the slot before it is refilled
         issue_next(stage);
         stage = (stage + 1) & (GE::STAGES - 1);
+        if (t_request) {
+            t_request = false;
+            t_issued = true;
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                if (lane + 32 * e < t_entries) t_early[e] = ld_relaxed_u64(t_entry(a, M, lane + 32 * e));
+        }
     }
     cp_async_wait<0>();
     QTRACE(4);
-    // Table of residual projections t[q][m] in shared memory, built by whichever warp leaves its
-    // main loop first, so that the global-memory latency hides behind the warps still computing.
-    if (a.rank > 0) {
-        int* t_builder = reinterpret_cast<int*>(smem + 20);
-        int mine = 0;
-        if (lane == 0) mine = atomicAdd(t_builder, 1) == 0;
-        mine = __shfl_sync(0xffffffffu, mine, 0);
-        if (mine) {
-            float* tt = reinterpret_cast<float*>(smem + p.off_tt);
-            if (p.t_inline) {
-                if (lane == 0) {                      // published long ago in practice; the wait is bounded
-                    const int want = a.rank * p.t_parts;
-                    int spins = 0;
-                    while (ld_acquire_s32(a.counters + (kWsMaxCounters - 2)) < want) {
-                        if (++spins > (1 << 22)) { atomicExch(a.counters + (kWsMaxCounters - 1), 1); break; }
-                        __nanosleep(64);
-                    }
-                }
-                __syncwarp();
-                for (int i = lane; i < a.rank * M; i += 32) {
-                    const int q = i / M, m = i - q * M;
-                    float v = 0.0f;
-                    for (int part = 0; part < p.t_parts; ++part) v += ld_cg_f32(a.tparts + (part * QGEMV_MAX_M + m) * kMaxRank + q);
-                    tt[i] = v;
-                }
-            } else {
-                pdl_wait();                           // t comes from the kernel launched just before this one
-                for (int i = lane; i < a.rank * M; i += 32) {
-                    const int q = i / M, m = i - q * M;
-                    tt[i] = ld_cg_f32(a.t + m * kMaxRank + q);
-                }
-            }
-        }
-    }
+    // Table of residual projections t[q][m] in shared memory, built by the last warp of the CTA.
+    if (a.rank > 0 && warp == p.nw - 1)
+        build_t_table<M>(p, smem, reinterpret_cast<float*>(ring), t_tag, t_early[0], t_early[1], t_issued);
     __syncthreads();                                  // every run of this CTA is parked, the table is complete
 
     // ---- tiles: add the runs in order, finish or hand over --------------------------------------
-    for (int tile = T0 + warp; tile <= T1; tile += p.nw) {
+    for (int tile = T0 + tw; tile <= T1; tile += p.nw) {
         const int lo = max(r0, tile * p.rpt), hi = min(r1, (tile + 1) * p.rpt);
+        const bool pre = efull && tile == etile;
         y[0] = y[1] = y[2] = y[3] = 0.f;
         if (t < TT) {
             for (int r = lo; r < hi; ++r) {
@@ -816,61 +936,19 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         }
         const bool whole = lo == tile * p.rpt && hi == (tile + 1) * p.rpt;
         if (whole) {
-            const bool pre = p.epi_async && tile == T0 + warp && (tile + 1) * kTileRows <= a.n;
             finish_tile<M, BF16>(p, smem, tile, y, pre ? epi : nullptr);
         } else {
-            // Tile shared with neighbouring CTAs: park this CTA's sum in global memory, count
-            // arrivals, and let the last CTA to arrive add the contributions in CTA order.
-            const int slot = tile == T0 ? 0 : 1;
-            float* mine = a.partial + ((size_t)(cta * 2 + slot) * 4) * 32;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) mine[i * 32 + lane] = y[i];
-            __threadfence();
-            __syncwarp();
-            const int cf = owner_of(tile * p.rpt, p.runs, grid);
-            const int cl = owner_of(tile * p.rpt + p.rpt - 1, p.runs, grid);
-            int last = 0;
-            if (lane == 0) {
-                const int old = atomicAdd(&a.counters[tile], 1);
-                last = old == cl - cf;
-                if (last) a.counters[tile] = 0;          // ready for the next launch
-            }
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence();
-                y[0] = y[1] = y[2] = y[3] = 0.f;
-                for (int cb = cf; cb <= cl; cb += 4) {     // four contributors' loads in flight at a time
-                    float v[4][4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int c = min(cb + k, cl);
-                        const int sl = tile == first_unit(c, p.runs, grid) / p.rpt ? 0 : 1;
-                        const float* src = a.partial + ((size_t)(c * 2 + sl) * 4) * 32;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) v[k][i] = ld_cg_f32(src + i * 32 + lane);
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        if (cb + k <= cl) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) y[i] += v[k][i];
-                        }
-                }
-                finish_tile<M, BF16>(p, smem, tile, y, nullptr);
-            }
+            shared_tile<M, BF16>(p, smem, tile, make_float4(y[0], y[1], y[2], y[3]), tile == T0 ? 0 : 1);
         }
     }
     QTRACE(5);
-    if (p.t_inline && a.rank > 0) {
-        // The last CTA to get here puts the two residual counters back to zero for the next launch.
-        __syncthreads();
-        if (tid == 0) {
-            __threadfence();
-            const int old = atomicAdd(a.counters + (kWsMaxCounters - 3), 1);
-            if (old == (int)gridDim.x - 1) {
-                a.counters[kWsMaxCounters - 2] = 0;
-                a.counters[kWsMaxCounters - 3] = 0;
-            }
+    if (p.t_inline && a.rank > 0 && tid == 0) {
+        // The last CTA to get here advances the launch count (every CTA has read it, and every reader
+        // has its projections) and clears the arrival counter for the next launch.
+        const int old = atomicAdd(a.counters + kWsDoneIdx, 1);
+        if (old == (int)gridDim.x - 1) {
+            a.counters[kWsEpochIdx] = (int)t_tag;
+            a.counters[kWsDoneIdx] = 0;
         }
     }
 }
@@ -957,7 +1035,7 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     pl.ng = p.k_padded / p.group;
     pl.nch = (pl.ng + cg - 1) / cg;
     pl.nt = (p.n + kTileRows - 1) / kTileRows;
-    if (pl.nt > kWsMaxCounters - 4) return pl;          // the last three counters are status / residual bookkeeping
+    if (pl.nt > kWsMaxCounters - 4) return pl;          // the last four counters are status / residual bookkeeping
     if ((long long)pl.nt * pl.nch > 0x3fffffff) return pl;
     const int sms = sm_count();
     // Runs: consecutive chunks of one tile.  One chunk per run unless a CTA would then need more
