@@ -60,6 +60,7 @@ struct MmaArgs {
     int rlen;          // chunks per run (a run = consecutive chunks of one tile, the unit of work)
     int rpt;           // runs per tile
     int runs;          // nt * rpt
+    int uq, urem;      // split of the work units (tiles or runs) over the CTAs: see first_unit()
     int scales_async;  // scale rows are aligned for 8/16-byte asynchronous copies
     int epi_async;     // outlier / residual rows are aligned for 16-byte asynchronous copies
     int ocb, rb;       // bytes per prefetched outlier-weight row / residual row (multiples of 16)
@@ -493,13 +494,15 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
     }
 }
 
-// First unit of part w, and the part that owns unit u, under the even split of `units` over `parts`
-// (units >= parts, so no part is empty; units < 2^31 and parts < 2^16, so the products fit 64 bits).
-__device__ __forceinline__ int first_unit(int w, int units, int parts) {
-    return (int)((unsigned long long)w * (unsigned)units / (unsigned)parts);
+// The work units (whole tiles, or runs) are split over the CTAs on the host: every CTA gets `uq`
+// units and the last `urem` CTAs one more (the first CTAs may carry a residual projection on top).
+// First unit of CTA c, and the CTA that owns unit u:
+__device__ __forceinline__ int first_unit(const MmaArgs& p, int c, int parts) {
+    return c * p.uq + max(0, c - (parts - p.urem));
 }
-__device__ __forceinline__ int owner_of(int u, int units, int parts) {
-    return (int)((((unsigned long long)u + 1) * (unsigned)parts - 1) / (unsigned)units);
+__device__ __forceinline__ int owner_of(const MmaArgs& p, int u, int parts) {
+    const int plain = parts - p.urem, thr = plain * p.uq;
+    return u < thr ? u / p.uq : plain + (u - thr) / (p.uq + 1);
 }
 
 // Address of entry idx = (part * rank + q) * M + m of the in-kernel residual projections.
@@ -581,8 +584,8 @@ __device__ __noinline__ void shared_tile(const MmaArgs& p, const unsigned char* 
     for (int i = 0; i < 4; ++i) mine[i * 32 + lane] = y[i];
     __threadfence();
     __syncwarp();
-    const int cf = owner_of(tile * p.rpt, p.runs, grid);
-    const int cl = owner_of(tile * p.rpt + p.rpt - 1, p.runs, grid);
+    const int cf = owner_of(p, tile * p.rpt, grid);
+    const int cl = owner_of(p, tile * p.rpt + p.rpt - 1, grid);
     int last = 0;
     if (lane == 0) {
         const int old = atomicAdd(&a.counters[tile], 1);
@@ -598,7 +601,7 @@ __device__ __noinline__ void shared_tile(const MmaArgs& p, const unsigned char* 
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int c = min(cb + k, cl);
-            const int sl = tile == first_unit(c, p.runs, grid) / p.rpt ? 0 : 1;
+            const int sl = tile == first_unit(p, c, grid) / p.rpt ? 0 : 1;
             const float* src = a.partial + ((size_t)(c * 2 + sl) * 4) * 32;
 #pragma unroll
             for (int i = 0; i < 4; ++i) v[k][i] = ld_cg_f32(src + i * 32 + lane);
@@ -630,9 +633,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     const int grid = gridDim.x, cta = blockIdx.x;
     // Whole tiles per CTA when that balances well enough (no tile is then shared between CTAs),
     // otherwise an even split of the runs.
-    const int r0 = p.tile_aligned ? first_unit(cta, p.nt, grid) * p.rpt : first_unit(cta, p.runs, grid);
-    const int r1 = p.tile_aligned ? first_unit(cta + 1, p.nt, grid) * p.rpt : first_unit(cta + 1, p.runs, grid);
-    const int T0 = r0 / p.rpt, T1 = (r1 - 1) / p.rpt;
+    const int u0 = first_unit(p, cta, grid), u1 = first_unit(p, cta + 1, grid);
+    const int r0 = p.tile_aligned ? u0 * p.rpt : u0, r1 = p.tile_aligned ? u1 * p.rpt : u1;
+    const int T0 = p.tile_aligned ? u0 : r0 / p.rpt, T1 = p.tile_aligned ? u1 - 1 : (r1 - 1) / p.rpt;
 
     unsigned char* ring = smem + p.off_ring + (size_t)warp * GE::STAGES * GE::STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring);
@@ -742,12 +745,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         if (efull) {
             const int opieces = p.ocb >> 4, upieces = p.rb >> 4;
             for (int i = lane; i < kTileRows * opieces; i += 32) {
-                const int r = i / opieces, c = i - r * opieces;
+                const int r = i % kTileRows, c = i / kTileRows;
                 cp_async16(smem_u32(epi) + r * p.ocb + c * 16,
                            reinterpret_cast<const unsigned char*>(a.ow + (size_t)(etile * kTileRows + r) * a.ldow) + c * 16);
             }
             for (int i = lane; i < kTileRows * upieces; i += 32) {
-                const int r = i / upieces, c = i - r * upieces;
+                const int r = i % kTileRows, c = i / kTileRows;
                 cp_async16(smem_u32(epi) + kTileRows * p.ocb + r * p.rb + c * 16,
                            reinterpret_cast<const unsigned char*>(a.ru + (size_t)(etile * kTileRows + r) * a.ldu) + c * 16);
             }
@@ -920,8 +923,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     QTRACE(4);
     // Table of residual projections t[q][m] in shared memory, built by the last warp of the CTA.
     if (a.rank > 0 && warp == p.nw - 1)
+    {
         build_t_table<M>(p, smem, reinterpret_cast<float*>(ring), t_tag, t_early[0], t_early[1], t_issued);
+        QTRACE(12);
+    }
     __syncthreads();                                  // every run of this CTA is parked, the table is complete
+    QTRACE(13);
 
     // ---- tiles: add the runs in order, finish or hand over --------------------------------------
     for (int tile = T0 + tw; tile <= T1; tile += p.nw) {
@@ -1107,6 +1114,8 @@ int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, cudaStream
     p.row_bytes = a.kpad * bits / 8;
     p.nw = pl.nw; p.stages = pl.stages;
     p.rlen = pl.rlen; p.rpt = pl.rpt; p.runs = pl.nt * pl.rpt;
+    const int units = pl.tile_aligned ? pl.nt : p.runs;
+    p.uq = units / pl.grid; p.urem = units % pl.grid;
     p.scales_async = pl.scales_async; p.epi_async = pl.epi_async; p.ocb = pl.ocb; p.rb = pl.rb;
     p.epi_bytes = pl.epi_bytes;
     p.off_xo = pl.off_xo; p.off_gx = pl.off_gx; p.off_slots = pl.off_slots; p.off_epi = pl.off_epi;
