@@ -155,7 +155,7 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
     do {                                                                                        \
         if ((threadIdx.x & 31) == 0) {                                                          \
             unsigned long long t_;                                                              \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory");                  \
             reinterpret_cast<unsigned long long*>(p.a.partial + (kMaxPartialFloats / 2))        \
                 [((size_t)blockIdx.x * 16 + (threadIdx.x >> 5)) * 16 + (slot)] = t_;            \
         }                                                                                       \
@@ -201,7 +201,7 @@ struct Geo {
 // scale the group so that it sits just below 2^14: fp16 then holds every multiplicand exactly
 // (or with an error far below fp32 rounding for elements 2^-20 times smaller than the largest).
 // ---------------------------------------------------------------------------------------------
-template <int BITS, int GB, int M, bool BF16, typename AfterLoads>
+template <int BITS, int GB, int M, bool BF16, bool EX, typename AfterLoads>
 __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned char* smem, AfterLoads after_loads) {
     using XT = typename Act16<BF16>::T;
     using GE = Geo<BITS, GB>;
@@ -241,16 +241,16 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
     };
 
     // outlier column indices (static data): first round held in a register
-    const int n_xo = a.oc * M;
+    const int n_xo = EX ? a.oc * M : 0;
     int col0 = -1;
-    if (tid < n_xo) col0 = a.oidx[tid / M];
+    if (EX && tid < n_xo) col0 = a.oidx[tid / M];
     QTRACE(10);
     load_items(0);
     QTRACE(11);
     // Residual projections t[m][c] = sum_k V[c,k] x[m,k], computed in-kernel: job j = (column c,
     // K-part) belongs to CTA j (there are never more jobs than CTAs).  Its loads are issued here,
     // with the activation loads, ahead of the weight prefetch.
-    const int t_jobs = p.t_inline ? a.rank * p.t_parts : 0;
+    const int t_jobs = (EX && p.t_inline) ? a.rank * p.t_parts : 0;
     const bool has_job = (int)blockIdx.x < t_jobs;
     const int t_part_k = nthr * 8;                 // columns of V one job covers: one 16-byte piece per thread
     uint4 tv = make_uint4(0u, 0u, 0u, 0u), tx[M];
@@ -412,8 +412,42 @@ __device__ __forceinline__ void epi_dot(const __half* w0, const __half* w1, cons
         }
     }
 }
+// The same for rows held in shared memory (16-byte aligned, cols a multiple of 8): lane t of the
+// quad owns columns 8t .. 8t+7 of every block of 32, so a row piece is one 16-byte load.
 template <int M>
-__device__ __forceinline__ void epi_dot_any(const __half* w0, const __half* w1, const float* v, int cols, int t,
+__device__ __forceinline__ void epi_dot_vec(const unsigned char* w0, const unsigned char* w1, const float* v, int cols, int t,
+                                            float (&e0)[M], float (&e1)[M]) {
+    for (int jb = 8 * t; jb < cols; jb += 32) {
+        const uint4 q0 = *reinterpret_cast<const uint4*>(w0 + jb * 2), q1 = *reinterpret_cast<const uint4*>(w1 + jb * 2);
+        const __half2* h0 = reinterpret_cast<const __half2*>(&q0);
+        const __half2* h1 = reinterpret_cast<const __half2*>(&q1);
+        float vv[8][M];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if constexpr (M == 4) {
+                const float4 q = *reinterpret_cast<const float4*>(v + (jb + i) * 4);
+                vv[i][0] = q.x; vv[i][1] = q.y; vv[i][2] = q.z; vv[i][3] = q.w;
+            } else if constexpr (M == 2) {
+                const float2 q = *reinterpret_cast<const float2*>(v + (jb + i) * 2);
+                vv[i][0] = q.x; vv[i][1] = q.y;
+            } else {
+#pragma unroll
+                for (int m = 0; m < M; ++m) vv[i][m] = v[(jb + i) * M + m];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f0 = __half22float2(h0[i]), f1 = __half22float2(h1[i]);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                e0[m] = fmaf(f0.x, vv[2 * i][m], e0[m]); e0[m] = fmaf(f0.y, vv[2 * i + 1][m], e0[m]);
+                e1[m] = fmaf(f1.x, vv[2 * i][m], e1[m]); e1[m] = fmaf(f1.y, vv[2 * i + 1][m], e1[m]);
+            }
+        }
+    }
+}
+template <int M>
+__device__ __noinline__ void epi_dot_any(const __half* w0, const __half* w1, const float* v, int cols, int t,
                                             float (&e0)[M], float (&e1)[M]) {
     if (cols <= 8) epi_dot<M, 2>(w0, w1, v, cols, t, e0, e1);
     else if (cols <= 16) epi_dot<M, 4>(w0, w1, v, cols, t, e0, e1);
@@ -439,30 +473,29 @@ __device__ __forceinline__ void epi_fold(float (&e0)[M], float (&e1)[M], int t, 
 // a launch starts with a cold instruction cache, and problems without these terms should not
 // have to step over their code.
 template <int M>
-__device__ __noinline__ float4 tile_extras(const MmaArgs& p, const unsigned char* smem, int tile, const unsigned char* pre) {
+__device__ __forceinline__ float4 tile_extras(const MmaArgs& p, const unsigned char* smem, int tile, const unsigned char* pre) {
     const Args& a = p.a;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int c0 = min(tile * kTileRows + g, a.n - 1), c1 = min(tile * kTileRows + g + 8, a.n - 1);
     float e0[M], e1[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) { e0[m] = 0.0f; e1[m] = 0.0f; }
-    if (a.oc > 0) {
-        const __half* ow0 = pre ? reinterpret_cast<const __half*>(pre + g * p.ocb) : a.ow + (size_t)c0 * a.ldow;
-        const __half* ow1 = pre ? reinterpret_cast<const __half*>(pre + (g + 8) * p.ocb) : a.ow + (size_t)c1 * a.ldow;
-        epi_dot_any<M>(ow0, ow1, reinterpret_cast<const float*>(smem + p.off_xo), a.oc, t, e0, e1);
-    }
-    if (a.rank > 0) {
-        const unsigned char* preu = pre ? pre + kTileRows * p.ocb : nullptr;
-        const __half* ru0 = pre ? reinterpret_cast<const __half*>(preu + g * p.rb) : a.ru + (size_t)c0 * a.ldu;
-        const __half* ru1 = pre ? reinterpret_cast<const __half*>(preu + (g + 8) * p.rb) : a.ru + (size_t)c1 * a.ldu;
-        epi_dot_any<M>(ru0, ru1, reinterpret_cast<const float*>(smem + p.off_tt), a.rank, t, e0, e1);
+    const float* xo = reinterpret_cast<const float*>(smem + p.off_xo);
+    const float* tt = reinterpret_cast<const float*>(smem + p.off_tt);
+    if (pre) {                                       // prefetched rows: 16-byte pieces
+        if (a.oc > 0) epi_dot_vec<M>(pre + g * p.ocb, pre + (g + 8) * p.ocb, xo, a.oc, t, e0, e1);
+        const unsigned char* preu = pre + kTileRows * p.ocb;
+        if (a.rank > 0) epi_dot_vec<M>(preu + g * p.rb, preu + (g + 8) * p.rb, tt, a.rank, t, e0, e1);
+    } else {
+        if (a.oc > 0) epi_dot_any<M>(a.ow + (size_t)c0 * a.ldow, a.ow + (size_t)c1 * a.ldow, xo, a.oc, t, e0, e1);
+        if (a.rank > 0) epi_dot_any<M>(a.ru + (size_t)c0 * a.ldu, a.ru + (size_t)c1 * a.ldu, tt, a.rank, t, e0, e1);
     }
     float y[4] = {0.f, 0.f, 0.f, 0.f};
     epi_fold<M>(e0, e1, t, y);
     return make_float4(y[0], y[1], y[2], y[3]);
 }
 
-template <int M, bool BF16>
+template <int M, bool BF16, bool EX>
 __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned char* smem, int tile, float (&y)[4],
                                             const unsigned char* pre) {
     using XT = typename Act16<BF16>::T;
@@ -470,9 +503,10 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int r0 = tile * kTileRows + g, r1 = r0 + 8;
     const int c0 = min(r0, a.n - 1), c1 = min(r1, a.n - 1);
-    if (a.oc > 0 || a.rank > 0) {
+    if constexpr (EX) {
         const float4 e = tile_extras<M>(p, smem, tile, pre);
         y[0] += e.x; y[1] += e.y; y[2] += e.z; y[3] += e.w;
+        QTRACE(15);
     }
     XT* out = static_cast<XT*>(a.y);
     float b0 = 0.0f, b1 = 0.0f;
@@ -574,7 +608,7 @@ __device__ __noinline__ void build_t_table(const MmaArgs& p, unsigned char* smem
 // A tile whose runs are split between neighbouring CTAs: this CTA parks its sum in global memory
 // and counts its arrival; the last CTA to arrive adds the contributions in CTA order and finishes
 // the tile.  Out of line: tile-aligned launches never come here.
-template <int M, bool BF16>
+template <int M, bool BF16, bool EX>
 __device__ __noinline__ void shared_tile(const MmaArgs& p, const unsigned char* smem, int tile, float4 sum, int slot) {
     const Args& a = p.a;
     const int lane = threadIdx.x & 31, grid = gridDim.x, cta = blockIdx.x;
@@ -613,13 +647,13 @@ __device__ __noinline__ void shared_tile(const MmaArgs& p, const unsigned char* 
                 for (int i = 0; i < 4; ++i) y[i] += v[k][i];
             }
     }
-    finish_tile<M, BF16>(p, smem, tile, y, nullptr);
+    finish_tile<M, BF16, EX>(p, smem, tile, y, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------
 // The kernel.  Persistent grid, blockDim.x = 32 * nw; every warp is its own producer and consumer.
 // ---------------------------------------------------------------------------------------------
-template <int BITS, int GB, int M, bool BF16>
+template <int BITS, int GB, int M, bool BF16, bool EX>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __grid_constant__ MmaArgs p) {
     using GE = Geo<BITS, GB>;
     constexpr int TT = (M + 1) / 2;                   // quad lanes that hold useful output columns
@@ -648,7 +682,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     constexpr int RPI = 32 / PPR;                    // rows covered by one warp-wide copy instruction
     const int lrow = lane / PPR, lcol = lane % PPR;
     // Runs are dealt round-robin: warp w takes runs r0 + w, r0 + w + nw, ...
-    const bool has_job = p.t_inline && (int)blockIdx.x < a.rank * p.t_parts;   // this CTA also computes a residual projection
+    const bool t_inline = EX && p.t_inline;
+    const bool has_job = t_inline && (int)blockIdx.x < a.rank * p.t_parts;   // this CTA also computes a residual projection
     constexpr int w0 = 0;
     const int nwk = p.nw;
     int pf_run = warp >= w0 ? r0 + warp - w0 : r1, pf_tile = 0, pf_j = 0, pf_ch = 0, pf_end = 0;   // pf_j: run index inside the tile
@@ -743,7 +778,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
                        (etile + 1) * kTileRows <= a.n;
     auto first_prefetch = [&]() {
         if (efull) {
-            const int opieces = p.ocb >> 4, upieces = p.rb >> 4;
+            const int opieces = EX ? p.ocb >> 4 : 0, upieces = EX ? p.rb >> 4 : 0;
             for (int i = lane; i < kTileRows * opieces; i += 32) {
                 const int r = i % kTileRows, c = i / kTileRows;
                 cp_async16(smem_u32(epi) + r * p.ocb + c * 16,
@@ -768,10 +803,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     QTRACE(9);
     // Tag of this launch for the residual projections that travel between CTAs (see below): the
     // workspace holds a launch count that the last CTA of every launch advances.
-    const bool t_reader = p.t_inline && warp == p.nw - 1;
+    const bool t_reader = t_inline && warp == p.nw - 1;
     unsigned t_tag = 0;
-    if (p.t_inline && (warp == 0 || t_reader)) t_tag = ld_relaxed_u32(a.counters + kWsEpochIdx) + 1u;
-    stage_activations<BITS, GB, M, BF16>(p, smem, [&]() {
+    if (t_inline && (warp == 0 || t_reader)) t_tag = ld_relaxed_u32(a.counters + kWsEpochIdx) + 1u;
+    stage_activations<BITS, GB, M, BF16, EX>(p, smem, [&]() {
         QTRACE(7);
         first_prefetch();
         QTRACE(1);
@@ -864,11 +899,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     };
 
     // Residual projections computed by other CTAs: a small table is requested by the reader warp
-    // after its first unit (the producers have published by then) and checked after the loop.
-    const int t_entries = p.t_inline ? p.t_parts * a.rank * M : 0;
+    // after its second unit (the producers have published by then) and checked after the loop.
+    const int t_entries = t_inline ? p.t_parts * a.rank * M : 0;
     unsigned long long t_early[2] = {0ull, 0ull};
     bool t_issued = false;
-    bool t_request = t_reader && t_entries <= 64;
+    int t_request = (t_reader && t_entries <= 64) ? 2 : 0;   // units to finish before the request goes out
 
     float y[4] = {0.f, 0.f, 0.f, 0.f};
     int stage = 0;
@@ -911,8 +946,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
         __syncwarp();                               // every lane is done reading the slot before it is refilled
         issue_next(stage);
         stage = (stage + 1) & (GE::STAGES - 1);
-        if (t_request) {
-            t_request = false;
+        if (t_request > 0 && --t_request == 0) {
             t_issued = true;
 #pragma unroll
             for (int e = 0; e < 2; ++e)
@@ -922,7 +956,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     cp_async_wait<0>();
     QTRACE(4);
     // Table of residual projections t[q][m] in shared memory, built by the last warp of the CTA.
-    if (a.rank > 0 && warp == p.nw - 1)
+    if (EX && a.rank > 0 && warp == p.nw - 1)
     {
         build_t_table<M>(p, smem, reinterpret_cast<float*>(ring), t_tag, t_early[0], t_early[1], t_issued);
         QTRACE(12);
@@ -942,14 +976,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
             }
         }
         const bool whole = lo == tile * p.rpt && hi == (tile + 1) * p.rpt;
+        QTRACE(14);
         if (whole) {
-            finish_tile<M, BF16>(p, smem, tile, y, pre ? epi : nullptr);
+            finish_tile<M, BF16, EX>(p, smem, tile, y, pre ? epi : nullptr);
         } else {
-            shared_tile<M, BF16>(p, smem, tile, make_float4(y[0], y[1], y[2], y[3]), tile == T0 ? 0 : 1);
+            shared_tile<M, BF16, EX>(p, smem, tile, make_float4(y[0], y[1], y[2], y[3]), tile == T0 ? 0 : 1);
         }
     }
     QTRACE(5);
-    if (p.t_inline && a.rank > 0 && tid == 0) {
+    if (t_inline && a.rank > 0 && tid == 0) {
         // The last CTA to get here advances the launch count (every CTA has read it, and every reader
         // has its projections) and clears the arrival counter for the next launch.
         const int old = atomicAdd(a.counters + kWsDoneIdx, 1);
@@ -976,9 +1011,9 @@ int sm_count() {
 
 inline int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
-template <int BITS, int GB, int M, bool BF16>
-int launch_one(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
-    auto kern = qgemv_mma_kernel<BITS, GB, M, BF16>;
+template <int BITS, int GB, int M, bool BF16, bool EX>
+int launch_ex(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
+    auto kern = qgemv_mma_kernel<BITS, GB, M, BF16, EX>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1004,6 +1039,14 @@ int launch_one(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) return check_launch("qgemv_mma_kernel");
     return check_launch("qgemv_mma_kernel");
+}
+
+// Problems without outlier columns and residual get a kernel that does not contain that code: a
+// launch starts with a cold instruction cache, and stepping over unused code is not free.
+template <int BITS, int GB, int M, bool BF16>
+int launch_one(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
+    if (p.a.oc > 0 || p.a.rank > 0) return launch_ex<BITS, GB, M, BF16, true>(p, grid, smem_bytes, s);
+    return launch_ex<BITS, GB, M, BF16, false>(p, grid, smem_bytes, s);
 }
 
 template <int BITS, int GB, int M>
