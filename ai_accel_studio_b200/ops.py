@@ -120,6 +120,37 @@ def _(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits, 
     return x.new_empty((x.shape[0], packed.shape[0]))
 
 
+def gemv_into(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+              outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
+              res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
+              bits: int, group: int, k_original: int, act: int, kernel: int, out: torch.Tensor) -> torch.Tensor:
+    """Same computation as ``gemv`` written into ``out`` ([M, N], x.dtype, unit inner stride).
+
+    ``out`` is a CUDA tensor on x's device or a *pinned* host tensor: pinned memory is addressable by
+    the device, so the kernel's stores then go straight to host memory and no separate device-to-host
+    copy is needed (worth it for results this small; the host must still wait for the stream before it
+    reads them).  A plain function, not a registered op: it mutates its argument and is meant for
+    serving loops, eager or captured in a CUDA graph."""
+    _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits)
+    if out.dtype != x.dtype or out.ndim != 2 or tuple(out.shape) != (x.shape[0], packed.shape[0]) or out.stride(1) != 1:
+        raise ValueError("out must be [M, N] of x.dtype with unit inner stride")
+    if out.is_cuda:
+        if out.device != x.device:
+            raise RuntimeError("out must be on x's device")
+    elif not out.is_pinned():
+        raise RuntimeError("a host result buffer must be pinned (page-locked) memory")
+    if outlier_idx is not None and outlier_idx.numel() == 0:
+        outlier_idx = outlier_weight = None
+    if res_u is not None and res_u.numel() == 0:
+        res_u = res_v = None
+    ws = ensure_workspace(x.device)
+    prob = _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, out, ws,
+                    bits, group, k_original, act, kernel)
+    with torch.cuda.device(x.device):
+        _cabi.run(prob, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
 @torch.library.custom_op("b200q::dequant", mutates_args=())
 def dequant(packed: torch.Tensor, scales: torch.Tensor, bits: int, group: int, k_original: int,
             dtype_name: str) -> torch.Tensor:

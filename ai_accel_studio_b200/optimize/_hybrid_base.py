@@ -133,6 +133,24 @@ class HybridPackedLinear(nn.Module):
                         self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
                         self.bits, self.group_size, self.original_k, 0, _cabi.KERNEL[self.kernel])
 
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Decode-path forward (at most 4 rows) written into ``out`` [M, out_features]: a CUDA tensor,
+        or a pinned host tensor that the kernel then writes directly (no device-to-host copy)."""
+        from .. import _cabi, ops
+        if not x.is_cuda:
+            raise RuntimeError(f"{type(self).__name__} computes on CUDA only (no CPU fallback); got a {x.device} tensor")
+        xflat = x.reshape(-1, x.shape[-1])
+        if xflat.shape[0] > 4:
+            raise ValueError("forward_into is the decode path: at most 4 rows")
+        xp = xflat if self.padded_k == self.original_k else F.pad(xflat, (0, self.padded_k - self.original_k))
+        if xp.stride(1) != 1:
+            xp = xp.contiguous()
+        has_o = self.outlier_idx.numel() > 0
+        return ops.gemv_into(xp, self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
+                             self.outlier_weight if has_o else None,
+                             self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
+                             self.bits, self.group_size, self.original_k, 0, _cabi.KERNEL[self.kernel], out)
+
     def _dense(self, xflat: torch.Tensor) -> torch.Tensor:
         from .. import ops
         name = str(xflat.dtype).split(".")[-1]

@@ -76,6 +76,34 @@ def test_int4_residual_extension():
     assert e_svd < e_plain
 
 
+def test_forward_into_device_and_pinned_host_buffers():
+    """forward_into writes the same bits as forward: into a device buffer, and straight into pinned
+    host memory (fast and general kernels, fp16 and bf16)."""
+    torch.manual_seed(3)
+    mods = [HybridInt2Linear(nn.Linear(1024, 1000), 128, None, 8, 8).cuda(),
+            HybridInt4Linear(nn.Linear(512, 96, bias=True), 128, None, 16).cuda(),
+            HybridInt4Linear(nn.Linear(1000, 333), 40, None, 5).cuda()]       # general kernel (odd group, ragged N)
+    for mod in mods:
+        for dt in (torch.float16, torch.bfloat16):
+            for m in (1, 4):
+                x = torch.randn(m, mod.in_features).to(dt).cuda()
+                want = mod(x)
+                dev_out = torch.full((m, mod.out_features), float("nan"), dtype=dt, device="cuda")
+                assert mod.forward_into(x, dev_out) is dev_out
+                assert torch.equal(dev_out, want)
+                host_out = torch.full((m, mod.out_features), float("nan"), dtype=dt).pin_memory()
+                mod.forward_into(x, host_out)
+                torch.cuda.synchronize()
+                assert torch.equal(host_out, want.cpu())
+    x = torch.randn(1, 512).half().cuda()
+    with pytest.raises(RuntimeError):
+        mods[1].forward_into(x, torch.empty((1, 96), dtype=torch.float16))            # pageable host memory
+    with pytest.raises(ValueError):
+        mods[1].forward_into(x, torch.empty((1, 97), dtype=torch.float16, device="cuda"))
+    with pytest.raises(ValueError):
+        mods[1].forward_into(torch.randn(5, 512).half().cuda(), torch.empty((5, 96), dtype=torch.float16, device="cuda"))
+
+
 def test_cuda_graph_capture_and_replay():
     torch.manual_seed(1)
     mods = [HybridInt2Linear(nn.Linear(1024, 1024), 128, None, 8, 4).cuda(),
