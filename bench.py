@@ -107,6 +107,13 @@ def load_c_oracle():
     l.qref_forward.argtypes = [vp, i64, ci, ci, vp, vp, i64, i64, i64, ci, ci, vp, vp, vp, ci, vp, vp, ci, ci, vp, vp]
     l.qref_forward.restype = None
     l.qref_num_threads.restype = ci
+    l.qref_set_threads.argtypes = [ci]
+    l.qref_set_threads.restype = None
+    try:                                         # all host cores this process may use, whatever OMP_NUM_THREADS says
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    l.qref_set_threads(cores)
     return l
 
 

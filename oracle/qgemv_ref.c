@@ -65,6 +65,15 @@ int qref_num_threads(void) {
 #endif
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timing run asks for the cores it may use. */
+void qref_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* codes[N, Kpad] <- packed; bits = 2: byte b holds columns 4b..4b+3 in bit pairs 0,2,4,6
  * (groupwise_int2.py:124); bits = 4: low nibble = even column (groupwise_int4.py:65). */
 void qref_unpack_codes(const uint8_t* packed, int64_t n, int64_t kpad, int bits, uint8_t* codes) {
