@@ -31,6 +31,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--compile-layers", action="store_true",
                     help="fuse the non-GEMV work of each decoder layer with torch.compile (regional compilation)")
+    ap.add_argument("--fuse-siblings", action="store_true",
+                    help="merge q/k/v and gate/up projections that share bit width and group size into one launch each")
     a = ap.parse_args()
 
     import torch.distributed as dist
@@ -45,7 +47,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     for variant in a.variants:
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
-                                  a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers)
+                                  a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers,
+                                  fuse_siblings=a.fuse_siblings)
         if world > 1:
             t = torch.tensor([res["decode_tokens_s"]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)          # the slowest rank sets the pace
@@ -58,7 +61,7 @@ def main():
                         fp16_bytes=res["fp16_bytes"],
                         weight_GBps_per_gpu=res["total"] * tps / a.batch / 1e9,
                         peak_vram_gb=res.get("peak_vram_gb"), cuda_graph=not a.no_graph,
-                        compiled_layers=a.compile_layers)
+                        compiled_layers=a.compile_layers, fused_sibling_groups=res.get("fused_sibling_groups", 0))
             print(json.dumps(line), flush=True)
         del res
         gc.collect()

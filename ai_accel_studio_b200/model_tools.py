@@ -163,7 +163,8 @@ def linear_weight_bytes(model) -> dict:
 
 
 def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
-                     mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False):
+                     mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False,
+                     fuse_siblings=False):
     """Build (this rank's slice of) the model, optionally apply the seeded mixed-bit plan, and run the
     fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts."""
     from .runtime_v5 import generate_static_benchmark
@@ -172,10 +173,15 @@ def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64,
         s = SHAPES[shape]
         plan = seeded_plan(model, probs, seed, global_k={"o_proj": s["heads"] * s["head_dim"], "down_proj": s["inter"]})
         apply_plan(model, plan, seed)
+    fused_groups = 0
+    if mixed and fuse_siblings:
+        from .optimize.siblings import fuse_decoder_siblings
+        fused_groups = fuse_decoder_siblings(model)
     g = torch.Generator().manual_seed(seed + 7)
     ids = torch.randint(0, SHAPES[shape]["vocab"], (batch, prompt_len), generator=g)
     res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=new_tokens, device=device,
                                     use_cuda_graph=use_cuda_graph, compile_layers=compile_layers)
     res.update(linear_weight_bytes(model))
     res["shape"], res["mixed"], res["world"] = shape, mixed, world
+    res["fused_sibling_groups"] = fused_groups
     return res

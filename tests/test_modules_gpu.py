@@ -104,6 +104,33 @@ def test_forward_into_device_and_pinned_host_buffers():
         mods[1].forward_into(torch.randn(5, 512).half().cuda(), torch.empty((5, 96), dtype=torch.float16, device="cuda"))
 
 
+def test_fused_siblings_match_separate_modules():
+    """q/k/v merged into one launch: the quantised term is the same arithmetic per row, the outlier
+    and residual terms are summed over the merged column lists -> equal within the kernel tolerance,
+    and equal to the oracle."""
+    from ai_accel_studio_b200.optimize.siblings import merge_packed
+    torch.manual_seed(5)
+    k = 1024
+    mods = []
+    for n, oc in ((512, 16), (128, 8), (128, 8)):
+        lin = nn.Linear(k, n, bias=False)
+        with torch.no_grad():
+            lin.weight[:, torch.randperm(k)[:8]] *= 6
+        m = HybridInt4Linear(lin, 128, None, oc)
+        m.set_residual(torch.randn(n, 8) * 0.03, torch.randn(8, k) * 0.03)
+        mods.append(m.cuda())
+    fused, sizes = merge_packed(mods)
+    for m_rows in (1, 4):
+        x = torch.randn(m_rows, k).half().cuda()
+        parts = fused(x).split(sizes, dim=-1)
+        for part, mod in zip(parts, mods):
+            pw = O.PackedWeight(4, mod.packed.cpu().numpy(), mod.scales.cpu().numpy(), k, k, 128)
+            ref = O.gemv_f32(x.cpu().numpy(), pw, None, mod.outlier_idx.cpu().numpy(), mod.outlier_weight.cpu().numpy(),
+                             mod.res_u.cpu().numpy(), mod.res_v.cpu().numpy())
+            assert_within_tolerance(part.float().cpu().numpy(), ref, "fused sibling slice vs oracle")
+            assert (part.float() - mod(x).float()).abs().max() < 2e-3
+
+
 def test_cuda_graph_capture_and_replay():
     torch.manual_seed(1)
     mods = [HybridInt2Linear(nn.Linear(1024, 1024), 128, None, 8, 4).cuda(),

@@ -1,0 +1,100 @@
+"""Sibling fusion on the CPU: the merged buffers describe the same function as the separate modules
+(checked with the oracle in float64), the merge refuses what it cannot express, and the rewiring of
+a decoder-shaped module tree calls the fused module once per activation tensor."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from oracle import qgemv_oracle as O
+from ai_accel_studio_b200.optimize import HybridInt2Linear, HybridInt4Linear
+from ai_accel_studio_b200.optimize.siblings import can_merge, fuse_decoder_siblings, merge_packed
+
+
+def _oracle(mod, x16):
+    pw = O.PackedWeight(mod.bits, mod.packed.numpy(), mod.scales.numpy(), mod.original_k, mod.padded_k, mod.group_size)
+    return O.gemv_f32(x16, pw,
+                      None if mod.bias is None else mod.bias.numpy(),
+                      mod.outlier_idx.numpy() if mod.outlier_idx.numel() else None,
+                      mod.outlier_weight.numpy() if mod.outlier_idx.numel() else None,
+                      mod.res_u.numpy() if mod.residual_rank else None,
+                      mod.res_v.numpy() if mod.residual_rank else None)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_merged_buffers_equal_separate_modules(bits):
+    torch.manual_seed(bits)
+    k = 256
+    cls = HybridInt2Linear if bits == 2 else HybridInt4Linear
+    mods = []
+    for n, oc, bias in ((48, 8, True), (16, 4, False), (33, 0, False)):
+        lin = nn.Linear(k, n, bias=bias)
+        with torch.no_grad():
+            lin.weight[:, torch.randperm(k)[:6]] *= 8          # distinct heavy columns per sibling
+        m = cls(lin, 64, None, oc)
+        if n != 33:
+            m.set_residual(torch.randn(n, 8) * 0.05, torch.randn(8, k) * 0.05)
+        mods.append(m)
+    assert can_merge(mods)
+    fused, sizes = merge_packed(mods)
+    assert sizes == [48, 16, 33] and fused.out_features == 97 and type(fused) is cls
+    assert fused.outlier_idx.numel() % 8 == 0 and fused.residual_rank == 16
+    assert fused.bias is not None and torch.equal(fused.bias[48:], torch.zeros(49, dtype=torch.float16))
+    x = (torch.randn(3, k) * 2).half().numpy()
+    got = _oracle(fused, x)
+    want = np.concatenate([_oracle(m, x) for m in mods], axis=1)
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-9)
+
+
+def test_merge_refuses_mismatched_siblings():
+    torch.manual_seed(0)
+    a = HybridInt2Linear(nn.Linear(128, 16), 64, None, 4)
+    assert not can_merge([a])
+    assert not can_merge([a, HybridInt4Linear(nn.Linear(128, 16), 64, None, 4)])        # bit width
+    assert not can_merge([a, HybridInt2Linear(nn.Linear(128, 16), 32, None, 4)])        # group size
+    assert not can_merge([a, HybridInt2Linear(nn.Linear(256, 16), 64, None, 4)])        # K
+    assert not can_merge([a, nn.Linear(128, 16)])
+    with pytest.raises(ValueError):
+        merge_packed([a, nn.Linear(128, 16)])
+
+
+class _Attn(nn.Module):
+    def __init__(self, k):
+        super().__init__()
+        self.q_proj, self.k_proj, self.v_proj = nn.Linear(k, 32), nn.Linear(k, 8), nn.Linear(k, 8)
+        self.o_proj = nn.Linear(32, k)
+
+
+class _Mlp(nn.Module):
+    def __init__(self, k):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = nn.Linear(k, 64), nn.Linear(k, 64), nn.Linear(64, k)
+
+
+class _Layer(nn.Module):
+    def __init__(self, k):
+        super().__init__()
+        self.self_attn, self.mlp = _Attn(k), _Mlp(k)
+
+
+def test_rewiring_calls_the_fused_module_once_per_activation():
+    torch.manual_seed(1)
+    layer = _Layer(128)
+    for name in ("q_proj", "k_proj", "v_proj"):
+        setattr(layer.self_attn, name, HybridInt4Linear(getattr(layer.self_attn, name), 64, None, 4))
+    layer.mlp.gate_proj = HybridInt2Linear(layer.mlp.gate_proj, 64, None, 4)
+    layer.mlp.up_proj = HybridInt4Linear(layer.mlp.up_proj, 64, None, 4)            # differs: stays unfused
+    assert fuse_decoder_siblings(layer) == 1
+    assert isinstance(layer.mlp.gate_proj, HybridInt2Linear) and isinstance(layer.mlp.up_proj, HybridInt4Linear)
+    fused = layer.self_attn.q_proj.fused
+    assert fused.out_features == 48 and "self_attn.q_proj.fused.packed" in layer.state_dict()
+    assert not any(k.startswith("self_attn.k_proj") for k in layer.state_dict())
+    calls = []
+    fused.forward = lambda x: calls.append(x) or torch.arange(48.0).repeat(x.shape[0], 1)     # stand-in: no GPU here
+    x = torch.randn(2, 128)
+    q, kk, v = layer.self_attn.q_proj(x), layer.self_attn.k_proj(x), layer.self_attn.v_proj(x)
+    assert len(calls) == 1 and q.shape == (2, 32) and kk.shape == (2, 8) and v.shape == (2, 8)
+    assert float(kk[0, 0]) == 32.0 and float(v[0, 0]) == 40.0
+    x2 = torch.randn(2, 128)
+    layer.self_attn.q_proj(x2), layer.self_attn.k_proj(x2), layer.self_attn.v_proj(x2)
+    assert len(calls) == 2
