@@ -1091,21 +1091,27 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     // Runs: consecutive chunks of one tile.  One chunk per run unless a CTA would then need more
     // than 32 KB of shared memory for the partial sums of its runs.
     const int slot_bytes = 8 * ((p.m + 1) / 2) * 16;
+    // Fewer tiles than SMs: one CTA per tile (its 16 warps split K) instead of a full grid whose
+    // CTAs share tiles -- the hand-over through global memory costs ~4 us, more than the idle SMs
+    // do as long as one tile's bytes stream in about that time.
+    const long long tile_bytes = (long long)kTileRows * p.k_padded * p.bits / 8;
+    const int grid_cap = (pl.nt < sms && tile_bytes <= 160 * 1024) ? pl.nt : sms;
     int rlen = 1, rpt = pl.nch, grid = 0, slot_cap = 0;
     for (;; rlen *= 2) {
         rpt = (pl.nch + rlen - 1) / rlen;
         const long long runs = (long long)pl.nt * rpt;
-        grid = (int)(runs < sms ? runs : sms);
+        grid = (int)(runs < grid_cap ? runs : grid_cap);
         slot_cap = (int)((runs + grid - 1) / grid) + 1;
         if (slot_cap * slot_bytes <= 32768 || rlen >= pl.nch) break;
     }
     if (slot_cap * slot_bytes > 65536) return pl;
     pl.rlen = rlen; pl.rpt = rpt; pl.grid = grid;
-    // whole tiles per CTA if the busiest CTA then has at most 20 % more than the average
+    // whole tiles per CTA if the busiest CTA then has at most 20 % more than the average, or if it
+    // streams so little (<= 160 KB) that the imbalance costs less than sharing tiles would
     pl.tile_aligned = 0;
     if (pl.nt >= grid) {
         const int most = (pl.nt + grid - 1) / grid;
-        if ((long long)most * grid * 5 <= (long long)pl.nt * 6) pl.tile_aligned = 1;
+        if ((long long)most * grid * 5 <= (long long)pl.nt * 6 || most * tile_bytes <= 160 * 1024) pl.tile_aligned = 1;
     }
     if (pl.tile_aligned) slot_cap = ((pl.nt + grid - 1) / grid) * rpt;
     if (slot_cap * slot_bytes > 65536) return pl;

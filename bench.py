@@ -48,6 +48,12 @@ WORKLOADS = {
                      name="int4_gemv_M4_K4096_N11008_g128_plain"),
     "int2_big": dict(bits=2, m=1, n=14336, k=4096, group=128, outliers=32, rank=8,
                      name="int2_gemv_M1_K4096_N14336_g128_oc32_r8"),
+    "int2_tp": dict(bits=2, m=1, n=3584, k=8192, group=128, outliers=64, rank=8,
+                    name="int2_gemv_M1_K8192_N3584_g128_oc64_r8"),
+    "int2_kv": dict(bits=2, m=1, n=1024, k=4096, group=128, outliers=32, rank=8,
+                    name="int2_gemv_M1_K4096_N1024_g128_oc32_r8"),
+    "int2_q": dict(bits=2, m=1, n=4096, k=4096, group=128, outliers=32, rank=8,
+                   name="int2_gemv_M1_K4096_N4096_g128_oc32_r8"),
     "int2_down": dict(bits=2, m=1, n=4096, k=14336, group=128, outliers=64, rank=8,
                       name="int2_gemv_M1_K14336_N4096_g128_oc64_r8"),
 }
