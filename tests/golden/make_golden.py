@@ -69,7 +69,7 @@ def seeded_c2(seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (ai_accel_lab on its path)")
     ap.add_argument("--skip-full", action="store_true")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
