@@ -13,11 +13,12 @@ LIB_PATH = Path(__file__).resolve().parent / "libqgemv_b200.so"
 OK = 0
 ACT = {"none": 0, "relu": 1, "silu": 2, "swish": 2}
 F16, BF16, F32 = 0, 1, 2
-KERNEL = {"auto": 0, "simt": 1, "mma": 2}
+KERNEL = {"auto": 0, "simt": 1, "mma": 2, "mma_phased": 3}
+DEBUG_DROP_PROJECTIONS, DEBUG_NO_L2_HINT = 1, 2
 MAX_M = 4
-ABI_VERSION = 1
+ABI_VERSION = 2
 
-EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
+EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_plan_describe", "qgemv_workspace_status", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem")
 
 
@@ -26,7 +27,7 @@ class Problem(C.Structure):
     _fields_ = [
         ("bits", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k_padded", C.c_int32),
         ("k_original", C.c_int32), ("group", C.c_int32), ("act", C.c_int32), ("x_dtype", C.c_int32),
-        ("outliers", C.c_int32), ("rank", C.c_int32), ("kernel", C.c_int32), ("reserved", C.c_int32),
+        ("outliers", C.c_int32), ("rank", C.c_int32), ("kernel", C.c_int32), ("debug", C.c_int32),
         ("x", C.c_void_p), ("ldx", C.c_int64),
         ("packed", C.c_void_p), ("ldp", C.c_int64),
         ("scales", C.c_void_p), ("lds", C.c_int64),
@@ -38,6 +39,15 @@ class Problem(C.Structure):
         ("y", C.c_void_p), ("ldy", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
+
+
+class PlanInfo(C.Structure):
+    """``struct qgemv_plan_info``."""
+    _fields_ = [("family", C.c_int32), ("variant", C.c_int32), ("launches", C.c_int32), ("grid", C.c_int32),
+                ("warps", C.c_int32), ("smem_bytes", C.c_int32), ("tile_aligned", C.c_int32),
+                ("inline_projections", C.c_int32), ("ctas_per_sm", C.c_int32), ("stages", C.c_int32),
+                ("run_chunks", C.c_int32), ("runs_per_tile", C.c_int32), ("epilogue_tiles", C.c_int32),
+                ("l2_chunks", C.c_int32), ("projection_parts", C.c_int32), ("chunk_bytes", C.c_int32)]
 
 
 class QgemvError(RuntimeError):
@@ -69,6 +79,10 @@ def lib():
     l.qgemv_plan_name.restype = C.c_char_p
     l.qgemv_plan_launches.argtypes = [C.POINTER(Problem)]
     l.qgemv_plan_launches.restype = C.c_int
+    l.qgemv_plan_describe.argtypes = [C.POINTER(Problem), C.POINTER(PlanInfo)]
+    l.qgemv_plan_describe.restype = C.c_int
+    l.qgemv_workspace_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+    l.qgemv_workspace_status.restype = C.c_int
     l.qdequant.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
                            C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     l.qdequant.restype = C.c_int
@@ -110,6 +124,12 @@ def plan_launches(problem: Problem) -> int:
     if r < 0:
         raise QgemvError(r, last_error())
     return r
+
+
+def plan_describe(problem: Problem) -> PlanInfo:
+    info = PlanInfo()
+    check(lib().qgemv_plan_describe(C.byref(problem), C.byref(info)))
+    return info
 
 
 def run_static(problem: Problem, stream: int) -> None:

@@ -14,10 +14,21 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libqgemv_b200.so"
-SOURCES = ["qgemv_api.cu", "qgemv_simt.cu", "qgemv_mma.cu", "qdequant.cu"]
+# (source, extra defines, object name).  The two tensor-core-assisted kernels are compiled once per bit
+# width so that the objects build in parallel.
+UNITS = [
+    ("qgemv_api.cu", [], "qgemv_api.o"),
+    ("qgemv_simt.cu", [], "qgemv_simt.o"),
+    ("qdequant.cu", [], "qdequant.o"),
+    ("qgemv_mma.cu", ["-DQGEMV_INST_BITS=2"], "qgemv_mma_int2.o"),
+    ("qgemv_mma.cu", ["-DQGEMV_INST_BITS=4"], "qgemv_mma_int4.o"),
+    ("qgemv_pipe.cu", ["-DQGEMV_INST_BITS=2"], "qgemv_pipe_int2.o"),
+    ("qgemv_pipe.cu", ["-DQGEMV_INST_BITS=4"], "qgemv_pipe_int4.o"),
+]
+OBJDIR = CSRC / "build"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
 ]
 # No --use_fast_math: the dequantisation kernels must round exactly like IEEE arithmetic.
 
@@ -37,27 +48,46 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; return its path."""
-    if not force and not _stale():
-        return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd), flush=True)
-    res = subprocess.run(cmd, capture_output=True, text=True)
+def build(force: bool = False, verbose: bool = False, extra_flags: tuple = (), lib: Path = LIB) -> Path:
+    """Compile the library if it is missing or older than its sources; return its path.
+
+    ``extra_flags`` (e.g. ``("-DQGEMV_TRACE",)``) and ``lib`` let a measurement build sit beside the
+    product build; objects of such a build go to their own directory."""
+    if not force and not extra_flags and lib == LIB and not _stale():
+        return lib
+    nvcc = _nvcc()
+    objdir = OBJDIR if not extra_flags else OBJDIR.with_name("build_" + "".join(c for c in "".join(extra_flags) if c.isalnum()))
+    objdir.mkdir(parents=True, exist_ok=True)
+    procs = []
+    for src, defs, obj in UNITS:
+        cmd = [nvcc, *NVCC_FLAGS, *defs, *extra_flags, "-c", str(CSRC / src), "-o", str(objdir / obj)]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+            print(" ".join(cmd), flush=True)
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    failed = []
+    for cmd, pr in procs:
+        out, err = pr.communicate()
+        if pr.returncode != 0:
+            failed.append(f"{' '.join(cmd)}\n{out}\n{err}")
+        elif verbose:
+            print(err)
+    if failed:
+        raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
+    link = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", "-o", str(lib),
+            *[str(objdir / obj) for _, _, obj in UNITS]]
+    res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        print(res.stderr)
-    return LIB
+        raise RuntimeError(f"link failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], help="extra -D flag for a measurement build, e.g. QGEMV_TRACE")
+    ap.add_argument("--output", default=None, help="library path of a measurement build (default: the product library)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, tuple("-D" + d for d in a.define), Path(a.output) if a.output else LIB))
     sys.exit(0)

@@ -46,7 +46,7 @@ int validate(const qgemv_problem* p, size_t need) {
     if (!p->x || !p->packed || !p->scales || !p->y) { set_error("qgemv_run: x, packed, scales and y must be non-null"); return QGEMV_ERR_BAD_ARG; }
     if (p->act < QGEMV_ACT_NONE || p->act > QGEMV_ACT_SILU) { set_error("qgemv_run: unknown activation %d", p->act); return QGEMV_ERR_BAD_ARG; }
     if (p->x_dtype != QGEMV_F16 && p->x_dtype != QGEMV_BF16) { set_error("qgemv_run: activations must be fp16 or bf16"); return QGEMV_ERR_BAD_ARG; }
-    if (p->kernel < QGEMV_KERNEL_AUTO || p->kernel > QGEMV_KERNEL_MMA) { set_error("qgemv_run: unknown kernel selector %d", p->kernel); return QGEMV_ERR_BAD_ARG; }
+    if (p->kernel < QGEMV_KERNEL_AUTO || p->kernel > QGEMV_KERNEL_MMA_PHASED) { set_error("qgemv_run: unknown kernel selector %d", p->kernel); return QGEMV_ERR_BAD_ARG; }
     if (p->outliers < 0 || (p->outliers > 0 && (!p->outlier_idx || !p->outlier_w))) { set_error("qgemv_run: outliers=%d needs outlier_idx and outlier_w", p->outliers); return QGEMV_ERR_BAD_ARG; }
     if (p->rank < 0 || (p->rank > 0 && (!p->res_u || !p->res_v))) { set_error("qgemv_run: rank=%d needs res_u and res_v", p->rank); return QGEMV_ERR_BAD_ARG; }
     if (p->rank > kMaxRank) { set_error("qgemv_run: residual rank %d exceeds the limit of %d", p->rank, kMaxRank); return QGEMV_ERR_TOO_LARGE; }
@@ -101,13 +101,35 @@ extern "C" size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, in
     return kWsPartialOff + kMaxPartialFloats * sizeof(float);
 }
 
+namespace {
+
+// The kernel a valid problem gets: the pipelined tensor-core kernel, the phased one, or (ok == false)
+// the CUDA-core kernel.  `forced_missing` is set when the caller forced the MMA family and the shape
+// does not allow it.
+MmaPlan choose(const qgemv_problem& p, size_t partial_floats, bool* forced_missing) {
+    MmaPlan plan{};
+    *forced_missing = false;
+    if (p.kernel == QGEMV_KERNEL_SIMT) return plan;
+    plan = plan_mma(p, partial_floats);
+    if (!plan.ok) {
+        *forced_missing = p.kernel == QGEMV_KERNEL_MMA || p.kernel == QGEMV_KERNEL_MMA_PHASED;
+        return plan;
+    }
+    if (p.kernel != QGEMV_KERNEL_MMA_PHASED) {
+        const MmaPlan pipe = plan_pipe(p, plan);
+        if (pipe.ok) return pipe;
+    }
+    return plan;
+}
+
+}  // namespace
+
 extern "C" const char* qgemv_plan_name(const qgemv_problem* p) {
     if (validate(p, qgemv_workspace_bytes(0, 0, 0, 0, 0, 0)) != QGEMV_OK) return nullptr;
-    if (p->kernel != QGEMV_KERNEL_SIMT) {
-        const MmaPlan plan = plan_mma(*p, kMaxPartialFloats);
-        if (plan.ok) return plan.name;
-        if (p->kernel == QGEMV_KERNEL_MMA) return nullptr;
-    }
+    bool missing = false;
+    const MmaPlan plan = choose(*p, kMaxPartialFloats, &missing);
+    if (plan.ok) return plan.name;
+    if (missing) return nullptr;
     return simt_name(p->bits, p->m, simt_unit_bytes(*p));
 }
 
@@ -122,12 +144,11 @@ int run_checked(const qgemv_problem* p, void* stream, size_t need_bytes, size_t 
     Args a = make_args(*p, partial_floats);
     const bool bf16 = p->x_dtype == QGEMV_BF16;
 
-    MmaPlan plan{};
-    bool use_mma = false;
-    if (p->kernel != QGEMV_KERNEL_SIMT) {
-        plan = plan_mma(*p, partial_floats);
-        use_mma = plan.ok;
-        if (!use_mma && p->kernel == QGEMV_KERNEL_MMA) {
+    bool missing = false;
+    const MmaPlan plan = choose(*p, partial_floats, &missing);
+    const bool use_mma = plan.ok;
+    {
+        if (missing) {
             set_error("qgemv_run: the tensor-core-assisted kernel does not support this shape "
                       "(needs 16-byte aligned x and packed rows, group in {32,64,128} for INT4 or {64,128,256} for INT2, "
                       "at most 256 outlier columns, and M * k_padded small enough for shared memory)");
@@ -138,6 +159,7 @@ int run_checked(const qgemv_problem* p, void* stream, size_t need_bytes, size_t 
         const int r = launch_residual_t(a, bf16, s);
         if (r != QGEMV_OK) return r;
     }
+    if (use_mma && plan.variant == 2) return launch_pipe(a, p->bits, bf16, plan, p->debug, s);
     if (use_mma) return launch_mma(a, p->bits, bf16, plan, s);
     return launch_simt(a, p->bits, bf16, simt_unit_bytes(*p), s);
 }
@@ -196,16 +218,63 @@ extern "C" int qgemv_run_static(const qgemv_problem* p, void* stream) {
     return run_checked(&q, stream, kStaticScratchBytes, kStaticPartialFloats);
 }
 
-extern "C" int qgemv_plan_launches(const qgemv_problem* p) {
+extern "C" int qgemv_plan_describe(const qgemv_problem* p, qgemv_plan_info* out) {
+    if (!out) { set_error("qgemv_plan_describe: out is NULL"); return QGEMV_ERR_BAD_ARG; }
     const int v = validate(p, qgemv_workspace_bytes(0, 0, 0, 0, 0, 0));
     if (v != QGEMV_OK) return v;
-    bool inline_t = false;
-    if (p->kernel != QGEMV_KERNEL_SIMT) {
-        const MmaPlan plan = plan_mma(*p, kMaxPartialFloats);
-        if (!plan.ok && p->kernel == QGEMV_KERNEL_MMA) return QGEMV_ERR_SHAPE;
-        inline_t = plan.ok && plan.t_inline;
+    bool missing = false;
+    const MmaPlan plan = choose(*p, kMaxPartialFloats, &missing);
+    if (missing) { set_error("qgemv_plan_describe: the tensor-core-assisted kernels do not support this shape"); return QGEMV_ERR_SHAPE; }
+    *out = qgemv_plan_info{};
+    const bool inline_t = plan.ok && plan.t_inline;
+    out->launches = (p->rank > 0 && !inline_t) ? 2 : 1;
+    if (plan.ok) {
+        out->family = QGEMV_KERNEL_MMA;
+        out->variant = plan.variant;
+        out->grid = plan.grid;
+        out->warps = plan.nw;
+        out->smem_bytes = plan.smem_bytes;
+        out->tile_aligned = plan.tile_aligned;
+        out->inline_projections = inline_t ? 1 : 0;
+        out->ctas_per_sm = (plan.variant == 2 && 2 * (plan.smem_bytes + 1024) <= 233472) ? 2 : 1;
+        out->stages = plan.stages;
+        out->run_chunks = plan.rlen;
+        out->runs_per_tile = plan.rpt;
+        out->epilogue_tiles = plan.variant == 2 ? plan.epi_tiles : 0;
+        out->l2_chunks = plan.variant == 2 ? plan.l2_chunks : 0;
+        out->projection_parts = inline_t ? plan.t_parts : 0;
+        out->chunk_bytes = plan.variant == 2 ? plan.chunk : (plan.gb == 16 ? 128 : 256);
+    } else {
+        out->family = QGEMV_KERNEL_SIMT;
+        out->tile_aligned = 1;
     }
-    return (p->rank > 0 && !inline_t) ? 2 : 1;
+    return QGEMV_OK;
+}
+
+extern "C" int qgemv_plan_launches(const qgemv_problem* p) {
+    qgemv_plan_info info;
+    const int v = qgemv_plan_describe(p, &info);
+    return v != QGEMV_OK ? v : info.launches;
+}
+
+extern "C" int qgemv_workspace_status(const void* workspace, void* stream, int32_t* host_out) {
+    if (!host_out) { set_error("qgemv_workspace_status: host_out is NULL"); return QGEMV_ERR_BAD_ARG; }
+    const char* ws = static_cast<const char*>(workspace);
+    if (!ws) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || !g_static_scratch_addr[dev]) {
+            (void)cudaGetLastError();
+            *host_out = 0;                       // the built-in scratch has not been used on this device yet
+            return QGEMV_OK;
+        }
+        ws = static_cast<const char*>(g_static_scratch_addr[dev]);
+    }
+    int* word = reinterpret_cast<int*>(const_cast<char*>(ws) + kWsCounterOff) + kWsStatusIdx;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(host_out, word, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemsetAsync(word, 0, sizeof(int32_t), s) != cudaSuccess)
+        return check_launch("qgemv_workspace_status");
+    return QGEMV_OK;
 }
 
 extern "C" int qgemv_run(const qgemv_problem* p, void* stream) {

@@ -88,9 +88,15 @@ struct MmaPlan {
     int scales_async, epi_async, ocb, rb, epi_bytes;
     int smem_bytes;         // dynamic shared memory
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
+    int variant;            // 1: barrier-phased kernel (qgemv_mma.cu), 2: pipelined kernel (qgemv_pipe.cu)
+    int epi_tiles, t_pv, l2_chunks, off_cnt, off_red;   // pipelined kernel only (see MmaArgs)
+    int chunk;              // pipelined kernel: packed bytes per row per ring slot (128 or 256)
     const char* name;
 };
 MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats);
 int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& plan, cudaStream_t s);
+// The pipelined kernel takes the shapes whose CTAs own whole tiles; `base` is plan_mma's answer.
+MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base);
+int launch_pipe(const Args& a, int bits, bool bf16, const MmaPlan& plan, int debug, cudaStream_t s);
 
 }  // namespace qgemv

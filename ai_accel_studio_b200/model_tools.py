@@ -149,6 +149,78 @@ def apply_plan(model, plan, seed=0):
     return model
 
 
+@torch.no_grad()
+def build_mixed_model_streaming(shape: str, device, world: int = 1, layers: int | None = None, seed: int = 0,
+                                max_positions: int = 4096, probs=(0.6, 0.3, 0.1)):
+    """The seeded mixed-bit model (this rank's slice) built without ever holding the dense model: the
+    skeleton lives on the meta device, and every Linear is materialised (random N(0, 0.02) fp16),
+    quantised where the plan says so and dropped, one at a time.  Peak memory is the packed model plus
+    one dense Linear, so the 70B shape (139 GB in fp16, 26 GB packed) builds on a single GPU.
+    Returns ``(model, plan)``; same plan and residual factors as ``seeded_plan`` + ``apply_plan``
+    (the dense values differ: they are drawn per layer, not in construction order)."""
+    from transformers import AutoModelForCausalLM
+    cfg = local_config(shape, world, layers, max_positions)
+    with torch.device("meta"):
+        model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
+    model.eval()
+    s = SHAPES[shape]
+    if world > 1:
+        for name, mod in list(model.named_modules()):
+            if isinstance(mod, nn.Linear) and name.split(".")[-1] in COLUMN_SPLIT:
+                _set(model, name, AllReduceLinear(mod))
+    plan = seeded_plan(model, probs, seed, global_k={"o_proj": s["heads"] * s["head_dim"], "down_proj": s["inter"]})
+    by_name = {e.name: e for e in plan}
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    g_res = torch.Generator(device="cpu").manual_seed(seed + 1)
+
+    def dense(meta_lin):
+        lin = nn.Linear(meta_lin.in_features, meta_lin.out_features, bias=meta_lin.bias is not None, device=dev, dtype=torch.float16)
+        lin.weight.normal_(0, 0.02, generator=gen)
+        if lin.bias is not None:
+            lin.bias.zero_()
+        return lin
+
+    for name, mod in list(model.named_modules()):
+        leaf = name.split(".")[-1]
+        holder = mod if isinstance(mod, AllReduceLinear) else None
+        lin = holder.inner if holder is not None else mod
+        if not isinstance(lin, nn.Linear) or (holder is None and isinstance(dict(model.named_modules()).get(name.rsplit(".", 1)[0]), AllReduceLinear)):
+            continue
+        new = dense(lin)
+        e = by_name.get(name)
+        if e is not None and e.bits != 16:
+            cls = HybridInt2Linear if e.bits == 2 else HybridInt4Linear
+            packed = cls(new, e.group_size, None, e.outlier_columns)
+            if e.residual_rank:
+                u = torch.randn(new.out_features, e.residual_rank, generator=g_res) * 0.01
+                v = torch.randn(e.residual_rank, new.in_features, generator=g_res) * 0.01
+                packed.set_residual(u.to(dev), v.to(dev))
+            packed.graph_safe = True
+            new = packed
+        if holder is not None:
+            holder.inner = new
+        else:
+            _set(model, name, new)
+    # what is still on the meta device: embeddings, norms, rotary tables
+    for name, mod in list(model.named_modules()):
+        if "rotary" in type(mod).__name__.lower() and any(b.is_meta for b in mod.buffers()):
+            _set(model, name, type(mod)(config=cfg, device=dev))
+    for name, prm in list(model.named_parameters()):
+        if prm.is_meta:
+            real = torch.empty(prm.shape, dtype=prm.dtype, device=dev)
+            if name.endswith("norm.weight") or "layernorm" in name:
+                real.fill_(1.0)
+            else:
+                real.normal_(0, 0.02, generator=gen)
+            parent, leaf = name.rsplit(".", 1)
+            setattr(dict(model.named_modules())[parent], leaf, nn.Parameter(real, requires_grad=False))
+    assert not any(t.is_meta for t in list(model.parameters()) + list(model.buffers())), "a tensor was left on the meta device"
+    if dev.type == "cuda":
+        torch.cuda.empty_cache()
+    return model, plan
+
+
 def linear_weight_bytes(model) -> dict:
     """Bytes of Linear-layer weights one decoded token must read (packed + fp16, lm_head included)."""
     packed = dense = 0

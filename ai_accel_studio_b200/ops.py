@@ -16,32 +16,71 @@ from . import _cabi
 _DT = {torch.float16: _cabi.F16, torch.bfloat16: _cabi.BF16, torch.float32: _cabi.F32}
 _DT_NAME = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}
 
-# One scratch buffer per device, shared by all calls issued on that device.  Calls are
-# stream-ordered in the decode path, and the kernels restore the buffer's invariant (all
-# split-K counters zero) before they finish, so it never needs clearing between calls.
-_WORKSPACE: dict[int, torch.Tensor] = {}
+# Scratch buffers.  A workspace must not be shared by GEMVs that can overlap on the device (it holds
+# the arrival counters and the launch tag of the residual projections), and calls on different
+# streams can overlap.  So every (device, stream) pair gets a workspace of its own.  Device memory may
+# not be allocated while a stream is being captured into a CUDA graph, therefore each device keeps a
+# small pool allocated ahead of time (by ``ensure_workspace``: module construction, ``.to(device)``
+# and the first eager call all run it) from which a stream that shows up during a capture is served.
+_POOL_SIZE = 4
+_POOL: dict[int, list] = {}                       # device index -> workspaces not yet bound to a stream
+_WORKSPACE: dict[tuple, torch.Tensor] = {}       # (device index, stream handle) -> its workspace
 
 
 def _device_index(dev: torch.device) -> int:
     return dev.index if dev.index is not None else torch.cuda.current_device()
 
 
-def ensure_workspace(device) -> torch.Tensor:
-    """Allocate (once, zero-filled) the per-device scratch buffer.  Must first run outside
-    CUDA-graph capture; module construction / ``.to(device)`` and the first eager call do."""
+def _new_workspace(idx: int) -> torch.Tensor:
+    nbytes = _cabi.workspace_bytes(4, _cabi.MAX_M, 1, 256, 128, 64)   # shape independent
+    return torch.zeros(nbytes, dtype=torch.uint8, device=torch.device("cuda", idx))
+
+
+def ensure_workspace(device, stream=None) -> torch.Tensor:
+    """The scratch buffer of ``stream`` (default: the current stream) on ``device``; zero-filled once.
+
+    The first call for a device, which allocates that device's pool, must come before any CUDA-graph
+    capture starts.  Later calls never allocate unless more than ``_POOL_SIZE`` streams of one device
+    have issued GEMVs, and then only outside a capture.  Calls issued on one stream are ordered, so
+    they share a workspace; calls on different streams get different ones and may overlap freely."""
     device = torch.device(device)
     if device.type != "cuda":
         raise RuntimeError("qgemv workspace lives in CUDA memory")
     idx = _device_index(device)
-    ws = _WORKSPACE.get(idx)
-    if ws is None:
-        if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("the qgemv scratch buffer must be created before CUDA-graph capture starts: "
+    handle = (stream if stream is not None else torch.cuda.current_stream(idx)).cuda_stream
+    ws = _WORKSPACE.get((idx, handle))
+    if ws is not None:
+        return ws
+    capturing = torch.cuda.is_current_stream_capturing()
+    pool = _POOL.get(idx)
+    if pool is None:
+        if capturing:
+            raise RuntimeError("the qgemv scratch buffers must be created before CUDA-graph capture starts: "
                                "call ai_accel_studio_b200.ops.ensure_workspace(device) first")
-        nbytes = _cabi.workspace_bytes(4, _cabi.MAX_M, 1, 256, 128, 64)   # shape independent
-        ws = torch.zeros(nbytes, dtype=torch.uint8, device=torch.device("cuda", idx))
-        _WORKSPACE[idx] = ws
+        pool = _POOL[idx] = [_new_workspace(idx) for _ in range(_POOL_SIZE)]
+    if not pool:
+        if capturing:
+            raise RuntimeError(f"more than {_POOL_SIZE} streams of one device issued packed GEMVs and the next one appeared "
+                               "during a CUDA-graph capture: call ensure_workspace(device, stream) for it before capturing")
+        pool.append(_new_workspace(idx))
+    ws = _WORKSPACE[(idx, handle)] = pool.pop()
     return ws
+
+
+def workspace_status(device, stream=None) -> int:
+    """Read and clear the sticky status word of a stream's workspace (synchronises that stream).
+    0: every GEMV since the last query completed normally; 1: a bounded wait inside a kernel ran out
+    (its result is not to be trusted; the workspace and the context stay usable)."""
+    import ctypes
+    device = torch.device(device)
+    idx = _device_index(device)
+    st = stream if stream is not None else torch.cuda.current_stream(idx)
+    ws = ensure_workspace(device, st)
+    out = ctypes.c_int32(-1)
+    with torch.cuda.device(idx):
+        _cabi.check(_cabi.lib().qgemv_workspace_status(ws.data_ptr(), st.cuda_stream, ctypes.byref(out)))
+        st.synchronize()
+    return int(out.value)
 
 
 def _require_cuda(t: torch.Tensor, name: str) -> None:
@@ -54,7 +93,8 @@ def _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v,
     m, kpad = x.shape
     p = _cabi.Problem()
     p.bits, p.m, p.n, p.k_padded, p.k_original, p.group = bits, m, packed.shape[0], kpad, k_original, group
-    p.act, p.x_dtype, p.kernel = act, _DT[x.dtype], kernel
+    p.act, p.x_dtype = act, _DT[x.dtype]
+    p.kernel, p.debug = kernel & 0xff, kernel >> 8       # bits 8+ carry qgemv_problem.debug (tests, benchmarks)
     p.x, p.ldx = x.data_ptr(), x.stride(0)
     p.packed, p.ldp = packed.data_ptr(), packed.stride(0)
     p.scales, p.lds = scales.data_ptr(), scales.stride(0)
@@ -100,7 +140,11 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Opti
          outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
          res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
          bits: int, group: int, k_original: int, act: int, kernel: int) -> torch.Tensor:
-    """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4."""
+    """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4.
+
+    Issued on the current stream with that stream's own scratch buffer (see ``ensure_workspace``), so
+    GEMVs on different streams may overlap.  ``kernel``: ``_cabi.KERNEL[...]``, optionally OR-ed with
+    ``debug_bits << 8``."""
     _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits)
     if outlier_idx is not None and outlier_idx.numel() == 0:
         outlier_idx = outlier_weight = None

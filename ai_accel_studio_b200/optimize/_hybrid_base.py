@@ -131,7 +131,11 @@ class HybridPackedLinear(nn.Module):
         return ops.gemv(xp, self.packed, self.scales, self.bias, self.outlier_idx if self.outlier_idx.numel() else None,
                         self.outlier_weight if self.outlier_idx.numel() else None,
                         self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
-                        self.bits, self.group_size, self.original_k, 0, _cabi.KERNEL[self.kernel])
+                        self.bits, self.group_size, self.original_k, 0, self._kernel_code())
+
+    def _kernel_code(self) -> int:
+        from .. import _cabi
+        return _cabi.KERNEL[self.kernel] | (int(getattr(self, "debug", 0)) << 8)
 
     def forward_into(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """Decode-path forward (at most 4 rows) written into ``out`` [M, out_features]: a CUDA tensor,
@@ -149,7 +153,7 @@ class HybridPackedLinear(nn.Module):
         return ops.gemv_into(xp, self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
                              self.outlier_weight if has_o else None,
                              self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
-                             self.bits, self.group_size, self.original_k, 0, _cabi.KERNEL[self.kernel], out)
+                             self.bits, self.group_size, self.original_k, 0, self._kernel_code(), out)
 
     def _dense(self, xflat: torch.Tensor) -> torch.Tensor:
         from .. import ops

@@ -26,7 +26,9 @@ from .planner_v5 import LayerDecisionV5
 FORMAT = "ai-accel-studio-bundle-v5"
 
 
-def save_bundle(model, source_model_id, decisions, out_dir, extra=None, tokenizer=None):
+def save_bundle(model, tokenizer, source_model_id, decisions, out_dir, extra=None):
+    """Same positional order as the reference (ai_accel_lab/optimize/bundle.py:15); ``tokenizer`` may be
+    None (random-token benchmarks have none)."""
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
     manifest = {"format": FORMAT, "source_model": source_model_id,

@@ -257,7 +257,7 @@ def run_gpu_arm(args, w):
     xs_dev = [x.to(dev) for x in xs_host]
     ys_host = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _ in range(RING)]
     ops.ensure_workspace(dev)
-    kernel = _cabi.KERNEL[args.kernel]
+    kernel = _cabi.KERNEL[args.kernel] | (args.debug << 8)
 
     def gemv(i, x):
         s = sets[i]
@@ -277,6 +277,7 @@ def run_gpu_arm(args, w):
                 self.register_buffer("outlier_weight", torch.empty((n, 0), dtype=torch.float16, device=dev))
             self.original_k = self.padded_k = self.in_features = k
             self.group_size, self.out_features, self.graph_safe, self.kernel = w["group"], n, True, args.kernel
+            self.debug = args.debug
             self.bias = None
             self.residual_rank = w["rank"]
             self.res_u, self.res_v = s.get("res_u"), s.get("res_v")
@@ -433,7 +434,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma", "mma_phased"])
+    ap.add_argument("--debug", type=lambda v: int(v, 0), default=0,
+                    help="qgemv_problem.debug bits (tuning aids of the pipelined kernel; see include/qgemv_b200.h)")
     ap.add_argument("--e2e-mode", choices=["overlap", "serial"], default="overlap",
                     help="end-to-end leg: copies on their own streams overlapping the kernels, or everything on one stream")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

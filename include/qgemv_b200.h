@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define QGEMV_ABI_VERSION 1
+#define QGEMV_ABI_VERSION 2
 
 enum qgemv_status {
     QGEMV_OK = 0,
@@ -34,12 +34,28 @@ enum qgemv_status {
 enum qgemv_act { QGEMV_ACT_NONE = 0, QGEMV_ACT_RELU = 1, QGEMV_ACT_SILU = 2 };
 enum qgemv_dtype { QGEMV_F16 = 0, QGEMV_BF16 = 1, QGEMV_F32 = 2 };
 
-/* Which kernel family a call may use.  AUTO picks the tensor-core-assisted streaming kernel
- * when the shape allows it and the CUDA-core kernel otherwise; the other two force a family
- * (used by the tests and by the profiles that justify the choice). */
-enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_MMA = 2 };
+/* Which kernel family a call may use.  AUTO picks a tensor-core-assisted streaming kernel when
+ * the shape allows it and the CUDA-core kernel otherwise; SIMT and MMA force a family.  Within
+ * the MMA family the pipelined kernel (half an SM per CTA, weights prefetched before the wait for
+ * the previous kernel) serves every shape whose CTAs can own whole 16-row tiles and the
+ * barrier-phased kernel the rest; MMA_PHASED forces the latter (tests, A/B measurements). */
+enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_MMA = 2, QGEMV_KERNEL_MMA_PHASED = 3 };
 
 #define QGEMV_MAX_M 4
+
+/* qgemv_problem.debug bits.  DROP_PROJECTIONS makes the CTAs that compute the residual
+ * projections of a launch keep them to themselves and shortens the readers' wait to a few
+ * microseconds, so a test can watch the wait run out: the launch then finishes with an output
+ * that lacks a valid residual term and raises the workspace's status word.  Nothing faults and
+ * the workspace stays usable. */
+#define QGEMV_DEBUG_DROP_PROJECTIONS 1
+/* Tuning aids of the pipelined kernel (benchmarks only): do not announce the weights that follow
+ * the ring to L2; smaller ring slots; force the warps per CTA (1..8) or the ring depth per warp (2..8). */
+#define QGEMV_DEBUG_NO_L2_HINT 2
+#define QGEMV_DEBUG_CHUNK128 4   /* ring slots of 128 packed bytes per row instead of 256 */
+#define QGEMV_DEBUG_EARLY_TRIGGER 8   /* release the next launch at kernel entry instead of after the prologue */
+#define QGEMV_DEBUG_WARPS(n) (((n) & 0xff) << 8)
+#define QGEMV_DEBUG_STAGES(n) (((n) & 0xf) << 16)
 
 /* One fused GEMV:  y[m, n] = act( sum_k x[m,k] * level(code[n,k]) * scale[n, k/group]
  *                               + sum_j x[m, outlier_idx[j]] * outlier_w[n, j]
@@ -60,8 +76,14 @@ enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_M
  *   the call is issued: the kernel may start reading them before the preceding kernel of the
  *   stream has finished (it waits for that kernel only before it reads x).
  *   workspace  zero-initialised ONCE by the caller, at least qgemv_workspace_bytes() bytes,
- *              256-byte aligned, private to calls that may overlap on the device.  The
- *              kernels leave it ready for the next call (no memset between calls).
+ *              256-byte aligned, private to calls that may overlap on the device (calls on
+ *              different streams without ordering need a workspace each).  The kernels leave it
+ *              ready for the next call, so no memset is needed between calls: every arrival
+ *              counter is back at zero, while three bookkeeping words near the end of the counter
+ *              area keep their values on purpose -- the number of launches completed so far (the
+ *              tag of the residual projections that CTAs of one launch pass to each other), the
+ *              count of CTAs that have finished the current launch (zero between calls) and the
+ *              sticky status word that qgemv_workspace_status() reads.
  */
 typedef struct qgemv_problem {
     int32_t bits;            /* 2 or 4 */
@@ -74,7 +96,7 @@ typedef struct qgemv_problem {
     int32_t outliers;        /* oc */
     int32_t rank;            /* residual rank, <= 64 */
     int32_t kernel;          /* enum qgemv_kernel */
-    int32_t reserved;
+    int32_t debug;           /* 0 in production; QGEMV_DEBUG_* bits for the library's own tests */
     const void* x;           int64_t ldx;
     const uint8_t* packed;   int64_t ldp;    /* bytes per packed row */
     const void* scales;      int64_t lds;
@@ -113,6 +135,18 @@ int qgemv_run(const qgemv_problem* p, void* stream);
 #define QGEMV_STATIC_MAX_N 262128
 int qgemv_run_static(const qgemv_problem* p, void* stream);
 
+/* Every wait inside the kernels is bounded.  The only one is for the residual projections
+ * t = res_v . x that a few CTAs of a launch compute for all the others: a reader that does not see
+ * them within its limit (about 30 ms) goes on with whatever value it has and sets the sticky status
+ * word of the workspace to 1, so the launch ends and the context stays healthy, but that launch's
+ * output is not to be trusted.  This call enqueues, on `stream`, a 4-byte copy of the status word
+ * into *host_out (host memory; pinned if the copy is to be asynchronous) followed by a reset of
+ * the word to 0.  Synchronise the stream before reading *host_out: 0 = every launch since the
+ * last query completed normally.  `workspace` is the pointer given to qgemv_run, or NULL for the
+ * built-in scratch of qgemv_run_static on the current device.  Not capturable in a CUDA graph.
+ * It has no counterpart in the reference project (its kernels never wait on each other). */
+int qgemv_workspace_status(const void* workspace, void* stream, int32_t* host_out);
+
 /* Bytes of workspace qgemv_run needs for a problem of this shape (never 0; at most a few MB). */
 size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, int group, int rank);
 
@@ -124,6 +158,29 @@ const char* qgemv_plan_name(const qgemv_problem* p);
  * shapes of the fast one compute the residual projections in a small kernel of their own), or a
  * negative QGEMV_ERR_* if the problem is invalid.  No launch happens. */
 int qgemv_plan_launches(const qgemv_problem* p);
+
+/* What qgemv_run would do for `p`, for tests, benchmarks and capacity planning.  No launch happens.
+ * Returns QGEMV_OK or a negative QGEMV_ERR_* if the problem is invalid. */
+typedef struct qgemv_plan_info {
+    int32_t family;          /* QGEMV_KERNEL_SIMT or QGEMV_KERNEL_MMA */
+    int32_t variant;         /* MMA family: 1 = barrier-phased kernel, 2 = pipelined kernel; 0 otherwise */
+    int32_t launches;        /* as qgemv_plan_launches */
+    int32_t grid;            /* CTAs */
+    int32_t warps;           /* warps per CTA */
+    int32_t smem_bytes;      /* dynamic shared memory per CTA */
+    int32_t tile_aligned;    /* 1: every CTA owns whole 16-row tiles; 0: some tiles are shared between CTAs
+                                and meet in the workspace (partial sums + arrival counters) */
+    int32_t inline_projections;  /* 1: residual projections computed inside the fused kernel */
+    int32_t ctas_per_sm;     /* CTAs of this kernel (or of this and the next launch) one SM can hold */
+    int32_t stages;          /* MMA family: ring slots per warp */
+    int32_t run_chunks;      /* MMA family: chunks (128 or 256 packed bytes per row) per run, the unit of work of a warp */
+    int32_t runs_per_tile;
+    int32_t epilogue_tiles;  /* pipelined kernel: tiles per CTA whose epilogue operands are prefetched */
+    int32_t l2_chunks;       /* pipelined kernel: chunks per warp announced to L2 before the dependency wait */
+    int32_t projection_parts;/* K parts of the in-kernel residual projections (0 when they are not inline) */
+    int32_t chunk_bytes;     /* MMA family: packed bytes per row per ring slot */
+} qgemv_plan_info;
+int qgemv_plan_describe(const qgemv_problem* p, qgemv_plan_info* out);
 
 /* Dequantise to a dense [N, Korig] matrix of out_dtype (QGEMV_F16 / BF16 / F32), bit-identical to
  * the reference's torch expression `levels.to(dtype)[codes] * scales.to(dtype)[:, k // group]`.

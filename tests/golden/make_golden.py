@@ -20,7 +20,7 @@ quantisers to what the reference computes on the same seeded inputs:
 The reference publishes no golden vectors of its own for this path; its tests only
 assert shapes and inequalities (tests/test_groupwise_int2.py, tests/test_v4_hybrid.py,
 tests/test_v5_mixedbit.py in the reference).  Those structural facts are re-asserted in
-tests/test_reference_structure.py.
+tests/test_host_logic.py.
 """
 from __future__ import annotations
 

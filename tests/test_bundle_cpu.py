@@ -30,7 +30,7 @@ def test_bundle_round_trip(tmp_path):
     m.down_proj = HybridInt4Linear(m.down_proj, 64, None, 4)
     decisions = [_decision("q_proj", 2, 8, 4), _decision("down_proj", 4, 4, 0),
                  LayerDecisionV5("lm_head", "fp16", 16, 128, 0, 0, 0.0, 1.0, 1.0, 1.0, 1.0, 1.0, "kept")]
-    out = save_bundle(m, "toy/model", decisions, tmp_path / "b")
+    out = save_bundle(m, None, "toy/model", decisions, tmp_path / "b")
     manifest = json.loads((out / "accel_manifest.json").read_text())
     assert manifest["format"] == FORMAT == "ai-accel-studio-bundle-v5" and manifest["source_model"] == "toy/model"
     assert set(manifest["layers"][0]) == {"name", "method", "bits", "group_size", "outlier_columns", "residual_rank",

@@ -131,6 +131,40 @@ def test_fused_siblings_match_separate_modules():
             assert (part.float() - mod(x).float()).abs().max() < 2e-3
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_shards_on_one_device(world, coracle):
+    """Every row shard and every column shard of a packed module, run through the CUDA kernels on one
+    device: row shards concatenate to, and column shards (re-based outlier indices, zero-weight padding
+    columns, bias on rank 0 only, K/T-wide res_v) sum to, the unsharded module's oracle result."""
+    from conftest import c_forward
+    from ai_accel_studio_b200 import tp
+    torch.manual_seed(40 + world)
+    n, k = 1024, 4096
+    for cls in (HybridInt2Linear, HybridInt4Linear):
+        lin = nn.Linear(k, n, bias=True)
+        with torch.no_grad():
+            lin.weight.normal_(0, 0.02)
+            lin.weight[:, torch.randperm(k)[:40]] *= 5          # clear outlier columns, unevenly spread over K
+        full = cls(lin, 128, None, 32)
+        full.set_residual(torch.randn(n, 8) * 0.02, torch.randn(8, k) * 0.02)
+        np_ = lambda t_: t_.detach().cpu().numpy()
+        for m in (1, 4):
+            x = torch.randn(m, k).half()
+            ref = c_forward(coracle, x.numpy(), full.bits, np_(full.packed), np_(full.scales), k, 128, np_(full.bias),
+                            np_(full.outlier_idx), np_(full.outlier_weight), np_(full.res_u), np_(full.res_v))
+            rows = [tp.shard_rows(full, r, world).cuda()(x.cuda()) for r in range(world)]
+            assert_within_tolerance(torch.cat(rows, 1).float().cpu().numpy(), ref, f"{cls.__name__} row shards T={world} m={m}")
+            ks = k // world
+            cols = [tp.shard_cols(full, r, world) for r in range(world)]
+            assert len({c.outlier_idx.numel() for c in cols}) == 1           # common padded outlier count
+            assert all(c.bias is None for c in cols[1:]) and cols[0].bias is not None
+            parts = [c.cuda()(x[:, r * ks:(r + 1) * ks].cuda()).float() for r, c in enumerate(cols)]
+            total = torch.stack(parts).sum(0)                                  # what the all-reduce computes (fp32 here)
+            # every rank rounds its partial result to fp16 before the sum: allow that on top of the tolerance
+            assert np.abs(total.cpu().numpy() - ref).max() <= 1e-2 + 1e-3 * np.abs(ref).max() + world * 2.0 ** -11 * np.abs(ref).max()
+            assert np.linalg.norm(total.cpu().numpy() - ref) <= 2e-3 * np.linalg.norm(ref)
+
+
 def test_cuda_graph_capture_and_replay():
     torch.manual_seed(1)
     mods = [HybridInt2Linear(nn.Linear(1024, 1024), 128, None, 8, 4).cuda(),

@@ -41,12 +41,16 @@ def _problem(bits, m, n, k, group, oc, rank, seed):
     return p, t
 
 
-# shapes that exercise the scratch: residual projections (rank > 0) and tiles shared between CTAs
+# Shapes that exercise the scratch: residual projections passed between CTAs through it (rank > 0,
+# pipelined and phased kernels), the separate projection kernel of the general path (last case), and
+# one whose tiles are shared between CTAs (partial sums and arrival counters live in the scratch).
 CASES = [(4, 4, 2048, 4096, 128, 32, 8), (2, 1, 96, 8192, 128, 8, 8), (2, 3, 4096, 1024, 64, 0, 0),
-         (4, 2, 50, 200, 8, 5, 3)]
+         (4, 1, 2400, 14336, 128, 64, 8), (4, 2, 50, 200, 8, 5, 3)]
+SHARED_TILE_CASE = 3
 
 
-def test_static_scratch_matches_workspace_entry_point_twice():
+def test_static_scratch_matches_workspace_entry_point_twice(coracle):
+    from conftest import c_forward, assert_within_tolerance
     lib = _cabi.lib()
     stream = torch.cuda.current_stream().cuda_stream
     ws = torch.zeros(_cabi.workspace_bytes(4, 4, 1, 256, 128, 8), dtype=torch.uint8, device="cuda")
@@ -57,6 +61,8 @@ def test_static_scratch_matches_workspace_entry_point_twice():
             y_sta = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
             p.y, p.ldy = y_ref.data_ptr(), n
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+            if i == SHARED_TILE_CASE:
+                assert _cabi.plan_describe(p).tile_aligned == 0
             assert lib.qgemv_run(ctypes.byref(p), ctypes.c_void_p(stream)) == 0, _cabi.last_error()
             p.y = y_sta.data_ptr()
             p.workspace, p.workspace_bytes = None, 0          # ignored by the static entry point
@@ -67,6 +73,11 @@ def test_static_scratch_matches_workspace_entry_point_twice():
             assert torch.isfinite(y_sta.float()).all()
             assert float(diff.max()) <= 1e-2 + 1e-3 * float(y_ref.float().abs().max()), (rep, i, float(diff.max()))
             assert torch.equal(y_sta, y_ref), (rep, i)
+            if rep == 0:                       # ... and on its own feet: against the CPU oracle
+                h = {k_: v.cpu().numpy() for k_, v in keep.items()}
+                ref = c_forward(coracle, h["x"], bits, h["packed"], h["scales"], k, group, h["bias"], h.get("oidx"),
+                                h.get("ow"), h.get("ru"), h.get("rv"))
+                assert_within_tolerance(y_sta.float().cpu().numpy(), ref, f"static scratch case {i}")
             del keep
 
 
