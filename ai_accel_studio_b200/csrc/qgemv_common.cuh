@@ -89,7 +89,7 @@ struct MmaPlan {
     int smem_bytes;         // dynamic shared memory
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
     int variant;            // 1: barrier-phased kernel (qgemv_mma.cu), 2: pipelined kernel (qgemv_pipe.cu)
-    int epi_tiles, t_pv, l2_chunks, off_cnt, off_red;   // pipelined kernel only (see MmaArgs)
+    int epi_tiles, t_pv, l2_chunks, off_cnt, off_red, off_bar;   // pipelined kernel only (see MmaArgs)
     int chunk;              // pipelined kernel: packed bytes per row per ring slot (128 or 256)
     const char* name;
 };

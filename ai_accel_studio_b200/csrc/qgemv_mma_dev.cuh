@@ -37,6 +37,7 @@ struct MmaArgs {
     int debug;         // qgemv_problem.debug
     int off_cnt;       // per-tile arrival counters of the CTA, followed by the "table of t is ready" flag
     int off_red;       // per-warp partial sums of a residual-projection job
+    int off_bar;       // mbarriers: one per ring slot per warp, then one for the epilogue operands
 };
 
 namespace {

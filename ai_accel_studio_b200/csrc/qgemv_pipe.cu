@@ -14,6 +14,14 @@
 //    of its share to L2) BEFORE griddepcontrol.wait.  While launch n computes, launch n+1 already
 //    has ~60 KB per SM of its weights on chip or in flight: DRAM keeps streaming through the
 //    prologue and the tail of every launch, which is where the phased kernel left it idle.
+//  * The ring is filled by the bulk-copy engine (cp.async.bulk global -> shared, one copy per row per
+//    slot, completion counted in bytes on an mbarrier per slot), not by per-thread cp.async.  With two
+//    CTAs on an SM, the waiting CTA's 16-byte copies sat in the load/store queues that the running
+//    CTA's shared-memory loads also go through, and stalled them (measured with cp.async: the main
+//    loop of the running launch took 14 us instead of 3, a dependent 8-byte load 3 us).  A bulk copy
+//    is one instruction for a whole row and its traffic never enters those queues.  Bulk copies
+//    write contiguous bytes, so the bank-conflict-free layout is a per-row ROTATION (row r starts
+//    (r mod R) * 128/R bytes into its slot row, written as two copies) instead of an XOR swizzle.
 //  * After the wait only x-dependent work is left: load x (L2 hits), stage it in B-fragment order,
 //    gather the outlier activations, one CTA barrier, main loop.
 //  * No barrier after the main loop.  A warp that completes a run parks its partial sums and bumps
@@ -39,6 +47,7 @@ constexpr int kPipeWarps = 8;                 // warps per CTA the kernel is com
 constexpr int kPipeMaxStages = 8;             // ring descriptors reserved per warp
 constexpr int kSmemPerSm = 233472;            // 228 KB of shared memory per SM on sm_100
 constexpr int kHalfSmSmem = (kSmemPerSm - 2 * 1024) / 2;   // dynamic bytes that let two CTAs share an SM (1 KB per CTA is reserved)
+constexpr int kBarSpinLimit = 1 << 22;        // bound of the wait for a bulk copy (each probe blocks for a while in hardware)
 constexpr int kFlagSpinLimit = 1 << 22;       // bound of the in-CTA wait for the table of residual projections
 constexpr int kTagSpinLimit = 1 << 20;        // bound of the wait for another CTA's projection (about 30 ms)
 constexpr int kTagSpinLimitDebug = 1 << 7;    // ... with QGEMV_DEBUG_DROP_PROJECTIONS (a few microseconds)
@@ -68,20 +77,28 @@ __device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes
 __device__ __forceinline__ int ld_volatile_shared(const int* p) {
     int v; asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory"); return v;
 }
-// cp.async.wait_group takes an immediate: leave at most `pending` (0..8) groups of this thread in flight.
-__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
-    switch (pending) {
-        case 0: cp_async_wait<0>(); break;
-        case 1: cp_async_wait<1>(); break;
-        case 2: cp_async_wait<2>(); break;
-        case 3: cp_async_wait<3>(); break;
-        case 4: cp_async_wait<4>(); break;
-        case 5: cp_async_wait<5>(); break;
-        case 6: cp_async_wait<6>(); break;
-        case 7: cp_async_wait<7>(); break;
-        default: cp_async_wait<8>(); break;
-    }
+// mbarrier + bulk-copy wrappers (shared::cta addresses are 32-bit shared-window addresses).
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(arrivals) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+// Global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned) whose
+// completion is counted, in bytes, on the mbarrier at `bar`.  This CTA's own shared memory only.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy ones.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // Activation staging after the dependency wait (whole CTA, no barrier inside; the caller's barrier
@@ -354,10 +371,20 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     int* t_flag = cnt + (p.uq + 1);
     for (int i = tid; i < p.uq + 2; i += blockDim.x) cnt[i] = 0;
 
+    // ---- barriers ---------------------------------------------------------------------------------
+    // One mbarrier per ring slot of every warp (one arrival: the lane that announces the bytes), one
+    // for the CTA's prefetched epilogue operands.
+    const uint32_t bars_u32 = smem_u32(smem + p.off_bar) + warp * kPipeMaxStages * 8;
+    const uint32_t epi_bar = smem_u32(smem + p.off_bar) + kPipeWarps * kPipeMaxStages * 8;
+    if (lane == 0) {
+        for (int s = 0; s < nstages; ++s) mbar_init(bars_u32 + s * 8, 1);
+        if (warp == 0) mbar_init(epi_bar, 1);
+        fence_mbar_init();
+    }
+    fence_proxy_async();
+    __syncthreads();                                 // barriers and counters initialised before any copy can signal them
+
     // ---- producer side --------------------------------------------------------------------------
-    constexpr int PPR = GE::CB / 16;                 // 16-byte pieces per row of a full chunk
-    constexpr int RPI = 32 / PPR;                    // rows covered by one warp-wide copy instruction
-    const int lrow = lane / PPR, lcol = lane % PPR;
     const bool t_inline = EX && p.t_inline;
     const bool has_job = t_inline && (int)blockIdx.x < a.rank * p.t_parts;   // this CTA also computes a residual projection
     const int nwk = p.nw;
@@ -371,18 +398,15 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     } else {
         pf_run = -1;
     }
-    constexpr int NIT = kTileRows / RPI;
-    const size_t tile_stride = (size_t)kTileRows * a.ldp;
-    const size_t it_stride = (size_t)RPI * a.ldp;
-    const uint8_t* lane_src = a.packed + (size_t)lrow * a.ldp + lcol * 16;
-    uint32_t dst_off[NIT];
-#pragma unroll
-    for (int it = 0; it < NIT; ++it) {
-        const int r = it * RPI + lrow;
-        dst_off[it] = r * GE::PITCH + ((lcol ^ GE::swz(r)) << 4);
-    }
-    const __half* lane_sc = a.scales + (size_t)min(lane, kTileRows - 1) * a.lds;
-    const size_t sc_tile_stride = (size_t)kTileRows * a.lds;
+    // A slot holds 16 rows of CB packed bytes, each rotated by ROT(row) bytes inside its CB-byte
+    // slot row, followed by 16 bytes of scales per row: the 8 scales of the aligned block of 8 groups
+    // that contains the chunk's groups.  Copy items of one slot: item i < 16 is row i from its
+    // rotation point to the end of the slot row, 16 <= i < 32 the part of row i - 16 that wraps to the
+    // start, 32 <= i < 48 the scale block of row i - 32.  Lane l issues items l and l + 32.
+    constexpr int ROT_ROWS = GE::SWZ_ROWS, ROT_STEP = 128 / GE::SWZ_ROWS;   // row r starts (r % ROT_ROWS) * ROT_STEP bytes in
+    const int crow = lane & 15;                       // row of this lane's code item and of its scale item
+    const int crot = (crow % ROT_ROWS) * ROT_STEP;
+    const bool wraps = lane >= 16;                    // this lane's code item is the wrapped part
     const bool ragged_n = (a.n % kTileRows) != 0;
     // Step the (run, chunk) cursor of this warp to the next chunk it owns; false when there is none.
     auto advance = [&]() {
@@ -402,77 +426,59 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     auto issue_next = [&](int s) {
         if (advance()) {
             const int ngr = min(GE::CG, p.ng - pf_ch * GE::CG);
+            const int len = ngr * GB;                                  // packed bytes per row of this chunk
             const uint32_t sbase = ring_u32 + s * GE::STAGE_BYTES;
-            const bool edge = ragged_n && pf_tile == p.nt - 1;        // rows past N are clamped to the last row
-            if (ngr == GE::CG && !edge && p.scales_async) {
-                // common case, straight-line: NIT row-group copies by every lane + one scale copy by lanes 0..15
-                const uint8_t* src = lane_src + (size_t)pf_tile * tile_stride + (size_t)pf_ch * GE::CB;
-#pragma unroll
-                for (int it = 0; it < NIT; ++it) { cp_async16(sbase + dst_off[it], src); src += it_stride; }
-                const __half* ssrc = lane_sc + (size_t)pf_tile * sc_tile_stride + pf_ch * GE::CG;
-                const uint32_t sdst = sbase + GE::SCALE_OFF + lane * 16;
-                if (lane < kTileRows) {
-                    if constexpr (GE::CG == 8) cp_async16(sdst, ssrc);
-                    else if constexpr (GE::CG == 4) cp_async8(sdst, ssrc);
-                    else cp_async4(sdst, ssrc);
-                }
-            } else {
-                const int pieces = (ngr * GB) >> 4;
-                if (lcol < pieces) {
-                    const uint8_t* src = a.packed + (size_t)pf_ch * GE::CB + lcol * 16;
-#pragma unroll
-                    for (int it = 0; it < NIT; ++it) {
-                        const int row = min(pf_tile * kTileRows + it * RPI + lrow, a.n - 1);
-                        cp_async16(sbase + dst_off[it], src + (size_t)row * a.ldp);
-                    }
-                }
-                if (lane < kTileRows) {                   // this row's scales for the chunk
-                    const __half* src = a.scales + (size_t)min(pf_tile * kTileRows + lane, a.n - 1) * a.lds + pf_ch * GE::CG;
-                    if (p.scales_async && ngr == GE::CG) {
-                        const uint32_t dst = sbase + GE::SCALE_OFF + lane * 16;
-                        if constexpr (GE::CG == 8) cp_async16(dst, src);
-                        else if constexpr (GE::CG == 4) cp_async8(dst, src);
-                        else cp_async4(dst, src);
-                    } else {
-                        __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16);
-                        for (int i = 0; i < ngr; ++i) d[i] = __ldg(src + i);
-                    }
-                }
+            const uint32_t bar = bars_u32 + s * 8;
+            // rows past N (last, ragged tile) repeat the last row; their results are never stored
+            const int row = ragged_n ? min(pf_tile * kTileRows + crow, a.n - 1) : pf_tile * kTileRows + crow;
+            fence_proxy_async();                                       // this slot was read with ordinary loads a moment ago
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(kTileRows * len + (p.scales_async ? kTileRows * 16 : 0)));
+            __syncwarp();
+            {
+                const uint8_t* src = a.packed + (size_t)row * a.ldp + (size_t)pf_ch * GE::CB;
+                const int first = min(len, GE::CB - crot);             // bytes from the rotation point to the end of the slot row
+                if (!wraps) bulk_g2s(sbase + crow * GE::PITCH + crot, src, (uint32_t)first, bar);
+                else if (len > first) bulk_g2s(sbase + crow * GE::PITCH, src + first, (uint32_t)(len - first), bar);
+            }
+            if (p.scales_async) {
+                if (lane < kTileRows)
+                    bulk_g2s(sbase + GE::SCALE_OFF + lane * 16, a.scales + (size_t)row * a.lds + ((pf_ch * GE::CG) & ~7), 16u, bar);
+            } else if (lane < kTileRows) {                             // unaligned scale rows: plain loads, this row's groups of the chunk
+                const __half* src = a.scales + (size_t)row * a.lds + pf_ch * GE::CG;
+                __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16) + ((pf_ch * GE::CG) & 7);
+                for (int i = 0; i < ngr; ++i) d[i] = __ldg(src + i);
             }
             if (lane == 0) meta[s] = make_int4(pf_tile, pf_ch, pf_run - r0, pf_ch + 1 == pf_end);
             ++pf_ch;
         } else if (lane == 0) {
             meta[s] = make_int4(-1, 0, 0, 0);
         }
-        cp_async_commit();
     };
 
     // ---- everything that does not depend on the previous kernel -----------------------------------
-    // Oldest copy group: epilogue operands (outlier-weight rows, residual rows, bias) of the CTA's
-    // first tiles, issued by all threads; the barrier that ends the prologue makes them visible.
+    // Epilogue operands (outlier-weight rows, residual rows, bias) of the CTA's first tiles: one bulk
+    // copy per row, all counted on one barrier that every thread checks before the prologue ends.
     {
-        const int opieces = EX ? p.ocb >> 4 : 0, upieces = EX ? p.rb >> 4 : 0;
-        const int per_tile = kTileRows * (opieces + upieces) + (a.bias ? 2 : 0);
         const int full_tiles = a.n / kTileRows;                       // tiles that lie completely inside N
         const int npre = p.epi_async ? min(min(p.epi_tiles, ntl), max(0, full_tiles - T0)) : 0;
+        const int ocb = EX ? p.ocb : 0, rb = EX ? p.rb : 0, bb = a.bias ? 32 : 0;
+        if (tid == 0) mbar_arrive_expect_tx(epi_bar, (uint32_t)(npre * (kTileRows * (ocb + rb) + bb)));
+        __syncwarp();
         const uint32_t epi_u32 = smem_u32(smem + p.off_epi);
+        const int per_tile = 2 * kTileRows + 1;                       // items: 16 outlier rows, 16 residual rows, bias
         for (int i = tid; i < npre * per_tile; i += blockDim.x) {
             const int lt = i / per_tile, q = i - lt * per_tile;
             const int row0 = (T0 + lt) * kTileRows;
             const uint32_t dst = epi_u32 + lt * p.epi_bytes;
-            if (q < kTileRows * opieces) {
-                const int r = q % kTileRows, c = q / kTileRows;
-                cp_async16(dst + r * p.ocb + c * 16, reinterpret_cast<const unsigned char*>(a.ow + (size_t)(row0 + r) * a.ldow) + c * 16);
-            } else if (q < kTileRows * (opieces + upieces)) {
-                const int qq = q - kTileRows * opieces, r = qq % kTileRows, c = qq / kTileRows;
-                cp_async16(dst + kTileRows * p.ocb + r * p.rb + c * 16,
-                           reinterpret_cast<const unsigned char*>(a.ru + (size_t)(row0 + r) * a.ldu) + c * 16);
-            } else {
-                const int c = q - kTileRows * (opieces + upieces);
-                cp_async16(dst + kTileRows * (p.ocb + p.rb) + c * 16, reinterpret_cast<const unsigned char*>(a.bias + row0) + c * 16);
+            if (q < kTileRows) {
+                if (ocb) bulk_g2s(dst + q * ocb, a.ow + (size_t)(row0 + q) * a.ldow, (uint32_t)ocb, epi_bar);
+            } else if (q < 2 * kTileRows) {
+                const int r = q - kTileRows;
+                if (rb) bulk_g2s(dst + kTileRows * ocb + r * rb, a.ru + (size_t)(row0 + r) * a.ldu, (uint32_t)rb, epi_bar);
+            } else if (bb) {
+                bulk_g2s(dst + kTileRows * (ocb + rb), a.bias + row0, 32u, epi_bar);
             }
         }
-        cp_async_commit();
     }
     for (int s = 0; s < nstages; ++s) issue_next(s);
     // The chunks that follow the ring go to L2 now (one instruction per chunk: lanes 0..15 take a row
@@ -507,7 +513,12 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     unsigned t_tag = 0;
     if (t_inline && (warp == 0 || t_reader)) t_tag = ld_relaxed_u32(a.counters + kWsEpochIdx) + 1u;
     pipe_stage_x<BITS, GB, M, BF16, EX>(p, smem, cols);
-    cp_async_wait_dyn(nstages);                       // the epilogue operands (oldest group) have landed
+    {                                                 // the epilogue operands have landed (long ago, normally)
+        int spins = 0;
+        while (!mbar_try_wait(epi_bar, 0)) {
+            if (++spins > kBarSpinLimit) { atomicExch(a.counters + kWsStatusIdx, 2); break; }
+        }
+    }
     __syncthreads();                                  // staged activations, counters and operands visible to every warp
     if (!(p.debug & QGEMV_DEBUG_EARLY_TRIGGER)) pdl_launch_dependents();
     PTRACE(2);
@@ -533,7 +544,7 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     const uint32_t gx_a_u32 = smem_u32(smem + p.off_gx) + ma * 8, gx_b_u32 = smem_u32(smem + p.off_gx) + mb * 8;
     const uint32_t slots_u32 = smem_u32(slots) + (g * TT + t) * 16;
     const uint32_t meta_u32 = smem_u32(meta);
-    const int sw16 = GE::swz(g) << 4;
+    const int rot = (g % ROT_ROWS) * ROT_STEP;                      // rotation of rows g and g + 8 inside their slot rows
     const uint32_t lane_row_u32 = ring_u32 + g * GE::PITCH;         // row g of slot 0 (row g+8 is 8 rows further)
     const uint32_t lane_sc_u32 = ring_u32 + GE::SCALE_OFF + g * 16;
     const int ng_total = p.ng;
@@ -542,7 +553,7 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     // One group of one chunk: G = absolute group index, gi = group inside the chunk.
     auto do_group = [&](uint32_t rowa, uint32_t rowb, int gi, int G, float s0, float s1, float (&yy)[4]) {
         const int lo = gi * GB + t * GE::TB;                          // logical byte offset of this lane's bytes
-        const uint32_t off = (uint32_t)(((lo & ~15) ^ sw16) + (lo & 15));
+        const uint32_t off = (uint32_t)((lo + rot) & (GE::CB - 1));   // rotations are multiples of 4 * TB: a lane's bytes never wrap
         uint32_t w0[GE::TW], w1[GE::TW];
         if constexpr (GE::TW == 1) {
             w0[0] = lds32(rowa + off); w1[0] = lds32(rowb + off);
@@ -614,16 +625,24 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
 
     float y[4] = {0.f, 0.f, 0.f, 0.f};
     int stage = 0;
+    uint32_t phases = 0;                            // bit s: parity of the next completion of slot s's barrier
     bool first = true;
     for (;;) {
-        cp_async_wait_dyn(nstages - 1);         // all but the newest stages-1 groups are done: this slot has landed
-        __syncwarp();
+        __syncwarp();                               // lane 0's descriptor of this slot is visible
         const uint4 mt = lds128(meta_u32 + stage * 16);          // tile, chunk, slot, last-of-run
         if ((int)mt.x < 0) break;
+        {                                           // the slot's bytes have landed
+            const uint32_t bar = bars_u32 + stage * 8, parity = (phases >> stage) & 1u;
+            int spins = 0;
+            while (!mbar_try_wait(bar, parity)) {
+                if (++spins > kBarSpinLimit) { atomicExch(a.counters + kWsStatusIdx, 2); break; }
+            }
+            phases ^= 1u << stage;
+        }
         if (first) { PTRACE(3); first = false; }
         const int ch = (int)mt.y;
         const uint32_t rowa = lane_row_u32 + stage * GE::STAGE_BYTES, rowb = rowa + 8 * GE::PITCH;
-        const uint32_t sca = lane_sc_u32 + stage * GE::STAGE_BYTES, scb = sca + 8 * 16;
+        const uint32_t sca = lane_sc_u32 + stage * GE::STAGE_BYTES + (((uint32_t)ch * GE::CG) & 7u) * 2, scb = sca + 8 * 16;
         __align__(16) __half sc0[8], sc1[8];
         if constexpr (GE::CG == 8) {
             *reinterpret_cast<uint4*>(sc0) = lds128(sca); *reinterpret_cast<uint4*>(sc1) = lds128(scb);
@@ -679,7 +698,6 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
             }
         }
     }
-    cp_async_wait<0>();
     if (t_pending) publish_table();                 // a reader warp without work still owes the table
     PTRACE(5);
     if (t_inline && a.rank > 0 && tid == 0) {
@@ -781,7 +799,8 @@ MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base) {
     pl.nch = (pl.ng + cg - 1) / cg;
     {
         auto al0 = [](const void* q, size_t a) { return reinterpret_cast<uintptr_t>(q) % a == 0; };
-        pl.scales_async = (p.lds % cg == 0) && al0(p.scales, (size_t)cg * 2) ? 1 : 0;
+        // scale rows go through the bulk-copy engine in aligned blocks of 8 scales (16 bytes)
+        pl.scales_async = (p.lds % 8 == 0) && (pl.ng % 8 == 0) && al0(p.scales, 16) ? 1 : 0;
     }
     const int sms = sm_count();
     const int grid = pl.nt < sms ? pl.nt : sms;
@@ -819,6 +838,7 @@ MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base) {
     pl.off_slots = off; off = align_up(off + slot_cap * slot_bytes, 128);
     pl.off_xs = off;    off = align_up(off + p.m * p.k_padded * 2, 128);
     pl.off_meta = off;  off += kPipeWarps * kPipeMaxStages * 16;
+    pl.off_bar = off;   off = align_up(off + kPipeWarps * kPipeMaxStages * 8 + 8, 128);
     pl.off_epi = off;   off = align_up(off + epi_tiles * epi_bytes, 128);
     pl.off_ring = off;
     pl.epi_bytes = epi_bytes;
@@ -885,7 +905,7 @@ int launch_pipe(const Args& a, int bits, bool bf16, const MmaPlan& pl, int debug
     p.epi_bytes = pl.epi_bytes; p.epi_tiles = pl.epi_tiles;
     p.off_xo = pl.off_xo; p.off_gx = pl.off_gx; p.off_slots = pl.off_slots; p.off_epi = pl.off_epi;
     p.off_meta = pl.off_meta; p.off_xs = pl.off_xs; p.off_ring = pl.off_ring;
-    p.off_cnt = pl.off_cnt; p.off_red = pl.off_red; p.off_tt = pl.off_tt;
+    p.off_cnt = pl.off_cnt; p.off_red = pl.off_red; p.off_tt = pl.off_tt; p.off_bar = pl.off_bar;
     p.t_inline = pl.t_inline; p.t_parts = pl.t_parts; p.t_pv = pl.t_pv;
     p.l2_chunks = pl.l2_chunks;
     p.debug = debug;

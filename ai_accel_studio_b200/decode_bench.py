@@ -33,6 +33,10 @@ def main():
                     help="fuse the non-GEMV work of each decoder layer with torch.compile (regional compilation)")
     ap.add_argument("--fuse-siblings", action="store_true",
                     help="merge q/k/v and gate/up projections that share bit width and group size into one launch each")
+    ap.add_argument("--split", action="store_true",
+                    help="also replay the decode step without the all-reduces / without the packed GEMVs and report their share")
+    ap.add_argument("--replicated-lm-head", action="store_true",
+                    help="tensor parallel: keep the whole output projection on every rank instead of vocab / world rows")
     a = ap.parse_args()
 
     import torch.distributed as dist
@@ -48,20 +52,22 @@ def main():
     for variant in a.variants:
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
                                   a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers,
-                                  fuse_siblings=a.fuse_siblings)
+                                  fuse_siblings=a.fuse_siblings, split=a.split, shard_vocab=not a.replicated_lm_head)
         if world > 1:
-            t = torch.tensor([res["decode_tokens_s"]], device=dev, dtype=torch.float64)
+            t = torch.tensor([res["aggregate_decode_tokens_s"]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)          # the slowest rank sets the pace
-            res["decode_tokens_s"] = float(t[0])
+            res["aggregate_decode_tokens_s"] = float(t[0])
         if rank == 0:
-            tps = res["decode_tokens_s"]
+            tps = res["aggregate_decode_tokens_s"]
             line = dict(shape=a.shape, variant=variant, world=world, batch=a.batch, prompt_tokens=a.prompt,
                         new_tokens=res["generated_tokens"], layers=a.layers, decode_tokens_s=tps,
                         ttft_ms=res["ttft_ms"], weight_bytes_per_rank=res["total"], packed_bytes=res["packed_bytes"],
                         fp16_bytes=res["fp16_bytes"],
                         weight_GBps_per_gpu=res["total"] * tps / a.batch / 1e9,
                         peak_vram_gb=res.get("peak_vram_gb"), cuda_graph=not a.no_graph,
-                        compiled_layers=a.compile_layers, fused_sibling_groups=res.get("fused_sibling_groups", 0))
+                        compiled_layers=a.compile_layers, fused_sibling_groups=res.get("fused_sibling_groups", 0),
+                        all_reduces_per_token=res.get("all_reduces_per_token"), packed_gemvs_per_token=res.get("packed_gemvs_per_token"),
+                        lm_head_rows_per_rank=res.get("lm_head_rows_per_rank"), split_ms_per_token=res.get("split_ms_per_token"))
             print(json.dumps(line), flush=True)
         del res
         gc.collect()

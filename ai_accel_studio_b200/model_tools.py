@@ -221,6 +221,16 @@ def build_mixed_model_streaming(shape: str, device, world: int = 1, layers: int 
     return model, plan
 
 
+def fp16_weight_bytes(shape: str, world: int = 1) -> int:
+    """Bytes of the fp16 model's weights on one rank (Linear layers split ``world`` ways, embeddings
+    replicated, lm_head split by vocabulary rows)."""
+    s = SHAPES[shape]
+    h, i, v = s["hidden"], s["inter"], s["vocab"]
+    qkv = h * (s["heads"] + 2 * s["kv_heads"]) * s["head_dim"]
+    per_layer = (qkv + s["heads"] * s["head_dim"] * h + 3 * h * i) // world
+    return 2 * (s["layers"] * per_layer + v * h + v * h // world)
+
+
 def linear_weight_bytes(model) -> dict:
     """Bytes of Linear-layer weights one decoded token must read (packed + fp16, lm_head included)."""
     packed = dense = 0
@@ -234,17 +244,59 @@ def linear_weight_bytes(model) -> dict:
     return dict(packed_bytes=packed, fp16_bytes=dense, total=packed + dense)
 
 
+def shard_lm_head(model, world: int):
+    """Replace ``lm_head`` by this rank's ``vocab / world`` rows (random-init models: the rows are
+    simply drawn at the smaller size).  The decoder finds the greedy token with an all-gather of
+    (best logit, index) pairs (``StaticGraphDecoder(vocab_shard=...)``)."""
+    head = model.lm_head
+    v = head.out_features
+    if world <= 1:
+        return model
+    if v % world:
+        raise ValueError(f"vocabulary {v} is not divisible by the tensor-parallel size {world}")
+    dev = head.weight.device if not head.weight.is_meta else None
+    new = nn.Linear(head.in_features, v // world, bias=False, device=dev if dev is not None else "meta", dtype=torch.float16)
+    if dev is not None:
+        with torch.no_grad():
+            new.weight.normal_(0, 0.02)
+    model.lm_head = new
+    return model
+
+
+def _timed_decode(dec, ids, new_tokens):
+    """Prefill, then ``new_tokens - 1`` graph replays timed with CUDA events: (ms per decoded token, tokens)."""
+    first = dec.prefill(ids)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    rest = dec.decode(new_tokens - 1)
+    e1.record()
+    e1.synchronize()
+    return float(e0.elapsed_time(e1)) / max(1, new_tokens - 1), torch.cat([first, rest], 1)
+
+
 def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
                      mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False,
-                     fuse_siblings=False):
-    """Build (this rank's slice of) the model, optionally apply the seeded mixed-bit plan, and run the
-    fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts."""
-    from .runtime_v5 import generate_static_benchmark
-    model = build_fp16_model(shape, device, world, layers, seed, max_positions=prompt_len + new_tokens + 16)
+                     fuse_siblings=False, split=False, shard_vocab=True):
+    """Build (this rank's slice of) the model, optionally with the seeded mixed-bit plan, and run the
+    fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts.
+
+    ``split=True`` also replays the captured decode step without the all-reduces and without the
+    packed GEMVs and reports the per-token milliseconds each of them accounts for
+    (``split_ms_per_token``: ``packed_gemv``, ``all_reduce``, ``other``)."""
+    from .runtime_v5 import generate_static_benchmark, StaticGraphDecoder
+    from .optimize._hybrid_base import HybridPackedLinear
+    max_pos = prompt_len + new_tokens + 16
     if mixed:
-        s = SHAPES[shape]
-        plan = seeded_plan(model, probs, seed, global_k={"o_proj": s["heads"] * s["head_dim"], "down_proj": s["inter"]})
-        apply_plan(model, plan, seed)
+        model, _ = build_mixed_model_streaming(shape, device, world, layers, seed, max_pos, probs)
+    else:
+        model = build_fp16_model(shape, device, world, layers, seed, max_positions=max_pos)
+    vocab_shard = None
+    if world > 1 and shard_vocab:
+        shard_lm_head(model, world)
+        if model.lm_head.weight.is_meta:
+            raise RuntimeError("lm_head was left on the meta device")
+        vocab_shard = (int(torch.distributed.get_rank()), world)
     fused_groups = 0
     if mixed and fuse_siblings:
         from .optimize.siblings import fuse_decoder_siblings
@@ -252,8 +304,34 @@ def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64,
     g = torch.Generator().manual_seed(seed + 7)
     ids = torch.randint(0, SHAPES[shape]["vocab"], (batch, prompt_len), generator=g)
     res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=new_tokens, device=device,
-                                    use_cuda_graph=use_cuda_graph, compile_layers=compile_layers)
+                                    use_cuda_graph=use_cuda_graph, compile_layers=compile_layers, vocab_shard=vocab_shard)
+    dec = res.pop("decoder")
     res.update(linear_weight_bytes(model))
     res["shape"], res["mixed"], res["world"] = shape, mixed, world
     res["fused_sibling_groups"] = fused_groups
+    res["all_reduces_per_token"] = sum(isinstance(m, AllReduceLinear) for m in model.modules()) if world > 1 else 0
+    res["packed_gemvs_per_token"] = sum(isinstance(m, HybridPackedLinear) for m in model.modules())
+    res["lm_head_rows_per_rank"] = int(model.lm_head.out_features)
+    if split and use_cuda_graph and torch.device(device).type == "cuda":
+        ids_d = ids.to(device)
+        full, _ = _timed_decode(dec, ids_d, new_tokens)
+        parts = {}
+        for key, holder, attr in (("all_reduce", AllReduceLinear, "skip_collective"), ("packed_gemv", HybridPackedLinear, "skip_gemv")):
+            if (key == "all_reduce" and world <= 1) or (key == "packed_gemv" and not mixed):
+                parts[key] = 0.0
+                continue
+            setattr(holder, attr, True)
+            try:
+                d2 = StaticGraphDecoder(model, batch, prompt_len + new_tokens + 8, device=device, vocab_shard=vocab_shard)
+                d2.prefill(ids_d)
+                d2.capture()
+                without, _ = _timed_decode(d2, ids_d, new_tokens)
+            finally:
+                setattr(holder, attr, False)
+            parts[key] = max(0.0, full - without)
+            del d2
+        parts["other"] = max(0.0, full - parts["all_reduce"] - parts["packed_gemv"])
+        parts["total"] = full
+        res["split_ms_per_token"] = parts
+    del dec
     return res

@@ -254,3 +254,17 @@ def plan_launches(x, packed, scales, bits, group, k_original, outlier_idx=None, 
     p = _problem(x, packed, scales, None, outlier_idx, outlier_weight, res_u, res_v, y, ws, bits, group,
                  k_original, 0, _cabi.KERNEL[kernel])
     return _cabi.plan_launches(p)
+
+
+def plan_describe(x, packed, scales, bits, group, k_original, outlier_idx=None, outlier_weight=None,
+                  res_u=None, res_v=None, kernel=0) -> dict:
+    """What one call with these operands would launch (``qgemv_plan_describe``), as a dict; ``kernel`` is
+    the integer selector ``gemv`` takes."""
+    ws = ensure_workspace(x.device)
+    y = torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device=x.device)
+    p = _problem(x, packed, scales, None, outlier_idx, outlier_weight, res_u, res_v, y, ws, bits, group,
+                 k_original, 0, kernel)
+    info = _cabi.plan_describe(p)
+    d = {name: int(getattr(info, name)) for name, _ in _cabi.PlanInfo._fields_}
+    d["name"] = _cabi.plan_name(p)
+    return d

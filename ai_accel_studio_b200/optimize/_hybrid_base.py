@@ -48,6 +48,10 @@ class HybridPackedLinear(nn.Module):
 
     bits: int = 0
     residual_rank: int = 0
+    # Measurement aid: when set, the decode path (M <= 4) launches nothing and returns a zero buffer
+    # of the right shape, so that replaying a decode step with and without the packed GEMVs tells how
+    # much of the step they are.  Never set in production.
+    skip_gemv: bool = False
 
     def _finish_init(self, pw, k: int, n: int, source_bias):
         self.register_buffer("packed", pw.packed)
@@ -173,7 +177,13 @@ class HybridPackedLinear(nn.Module):
             raise RuntimeError("fp16/bf16 activations required")
         shape = x.shape
         xflat = x.reshape(-1, shape[-1])
-        if xflat.shape[0] <= 4:
+        if xflat.shape[0] <= 4 and HybridPackedLinear.skip_gemv:
+            key = (xflat.shape[0], x.dtype)
+            cache = self.__dict__.setdefault("_skip_out", {})
+            if key not in cache:
+                cache[key] = torch.zeros((xflat.shape[0], self.out_features), dtype=x.dtype, device=x.device)
+            y = cache[key]
+        elif xflat.shape[0] <= 4:
             xp = xflat if self.padded_k == self.original_k else F.pad(xflat, (0, self.padded_k - self.original_k))
             if xp.stride(1) != 1:
                 xp = xp.contiguous()

@@ -3,7 +3,7 @@
 Mirrors ``ai_accel_lab/runtime_v5.py`` of the reference project: ``prepare_static_compile``
 (:7-23) and ``generate_static_benchmark`` (:29-73, same timing protocol: warm-ups, one timed
 prefill = TTFT, one timed fixed-length greedy generation, decode tok/s = generated /
-(total - TTFT)).  Two things differ:
+(total - TTFT)).  These things differ:
 
 * Token ids can be passed directly (``input_ids=``): the benchmark configurations use random
   prompts, and no tokenizer files are needed for them.
@@ -12,6 +12,15 @@ prefill = TTFT, one timed fixed-length greedy generation, decode tok/s = generat
   going through ``torch.compile(mode='reduce-overhead')``.  ``prepare_static_compile`` is kept
   for callers that want the reference's compiled path; the packed ops are registered custom ops
   with fake kernels, so Dynamo traces through them.
+* Prompts that would need padding (a batch of texts of different lengths, or a length that is not
+  a multiple of 8) are refused on the tokenizer path: the decoder keeps no attention mask, and
+  attending to pad tokens would change the tokens and the TTFT.  Pass ``input_ids`` of equal length.
+* ``decode_tokens_s`` / ``total_tokens_s`` are per sequence, as in the reference
+  (generated / time); the whole-batch rates are reported as ``aggregate_decode_tokens_s`` /
+  ``aggregate_total_tokens_s``.
+* Under tensor parallelism the output projection can be split by vocabulary rows
+  (``vocab_shard=(rank, world)``): every rank then holds ``vocab / world`` rows of ``lm_head``, and
+  the greedy token is found with one small all-gather of each rank's (best logit, index) pair.
 """
 from __future__ import annotations
 
@@ -71,9 +80,12 @@ class StaticGraphDecoder:
     synchronisation in between and returns the ``[B, n]`` tokens.
     """
 
-    def __init__(self, model, batch_size: int, max_cache_len: int, device=None, dtype=None, compile_layers=False):
+    def __init__(self, model, batch_size: int, max_cache_len: int, device=None, dtype=None, compile_layers=False,
+                 vocab_shard=None, group=None):
         from transformers import StaticCache
         self.model = model
+        self.vocab_rank, self.vocab_world = vocab_shard if vocab_shard is not None else (0, 1)
+        self.group = group
         if compile_layers:
             compile_decoder_layers(model)
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
@@ -88,10 +100,23 @@ class StaticGraphDecoder:
         self.graph = None
         self.out_tok = None
 
+    def _greedy(self, last_logits: torch.Tensor) -> torch.Tensor:
+        """Arg-max over the vocabulary, [B, V or V / world] -> [B, 1]; with a vocabulary-sharded output
+        projection the ranks exchange their (best logit, global index) pairs."""
+        if self.vocab_world <= 1:
+            return last_logits.argmax(-1, keepdim=True)
+        val, idx = last_logits.float().max(-1)
+        mine = torch.stack([val, (idx + self.vocab_rank * last_logits.shape[-1]).float()], -1)      # [B, 2]; indices < 2^24 are exact
+        flat = torch.empty((self.vocab_world * mine.shape[0], 2), dtype=mine.dtype, device=mine.device)
+        torch.distributed.all_gather_into_tensor(flat, mine, group=self.group)
+        every = flat.view(self.vocab_world, mine.shape[0], 2)
+        best = every[..., 0].argmax(0)                                                               # first maximum: lowest rank, lowest index
+        return every[best, torch.arange(mine.shape[0], device=mine.device), 1].long().unsqueeze(-1)
+
     @torch.no_grad()
     def _step(self):
         out = self.model(input_ids=self.tok, past_key_values=self.cache, cache_position=self.pos, use_cache=True)
-        nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+        nxt = self._greedy(out.logits[:, -1])
         self.tok.copy_(nxt)
         self.pos.add_(1)
         return nxt
@@ -104,7 +129,7 @@ class StaticGraphDecoder:
         self.cache.reset()
         out = self.model(input_ids=input_ids, past_key_values=self.cache,
                          cache_position=torch.arange(n, device=self.device), use_cache=True)
-        nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+        nxt = self._greedy(out.logits[:, -1])
         self.tok.copy_(nxt)
         self.pos.fill_(n)
         return nxt
@@ -146,7 +171,7 @@ class StaticGraphDecoder:
 
 @torch.no_grad()
 def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens=64, device="cuda", warmups=2,
-                              input_ids=None, use_cuda_graph=True, compile_layers=False):
+                              input_ids=None, use_cuda_graph=True, compile_layers=False, vocab_shard=None, group=None):
     """Fixed-length greedy generation benchmark (reference protocol, ai_accel_lab/runtime_v5.py:29-73).
 
     Either ``tokenizer`` + ``prompt`` (left-padded to a multiple of 8, as the reference does) or
@@ -160,12 +185,18 @@ def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens
         tokenizer.padding_side = "left"
         if getattr(tokenizer, "pad_token_id", None) is None and getattr(tokenizer, "eos_token_id", None) is not None:
             tokenizer.pad_token_id = tokenizer.eos_token_id
-        input_ids = tokenizer(prompt, return_tensors="pt", padding=True, pad_to_multiple_of=8)["input_ids"]
+        enc = tokenizer(prompt, return_tensors="pt", padding=True, pad_to_multiple_of=8)
         tokenizer.padding_side = old
+        input_ids = enc["input_ids"]
+        mask = enc.get("attention_mask") if hasattr(enc, "get") else None
+        if mask is not None and not bool(mask.bool().all()):
+            raise NotImplementedError("this prompt needs padding (left-padded to a multiple of 8): the static decoder keeps no "
+                                      "attention mask, so pad tokens would be attended to; pass input_ids of equal length")
     input_ids = input_ids.to(device)
     b, n = input_ids.shape
     cuda = torch.device(device).type == "cuda"
-    dec = StaticGraphDecoder(model, b, n + int(max_new_tokens) + 8, device=device, compile_layers=compile_layers)
+    dec = StaticGraphDecoder(model, b, n + int(max_new_tokens) + 8, device=device, compile_layers=compile_layers,
+                             vocab_shard=vocab_shard, group=group)
 
     for _ in range(max(1, int(warmups))):
         dec.prefill(input_ids)
@@ -198,8 +229,10 @@ def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens
     generated = int(out.shape[1])
     decode_ms = max(0.001, total_ms - ttft)
     res = dict(prompt_tokens=n, generated_tokens=generated, ttft_ms=ttft,
-               decode_tokens_s=b * generated / (decode_ms / 1000.0), total_tokens_s=b * generated / (total_ms / 1000.0),
-               batch=b, tokens=out)
+               decode_tokens_s=generated / (decode_ms / 1000.0), total_tokens_s=generated / (total_ms / 1000.0),
+               aggregate_decode_tokens_s=b * generated / (decode_ms / 1000.0),
+               aggregate_total_tokens_s=b * generated / (total_ms / 1000.0),
+               decode_ms_per_token=decode_ms / generated, batch=b, tokens=out, decoder=dec)
     if cuda:
         res.update(peak_vram_gb=torch.cuda.max_memory_allocated() / 1024 ** 3,
                    current_vram_gb=torch.cuda.memory_allocated() / 1024 ** 3,

@@ -103,7 +103,13 @@ def shard_cols(mod: HybridPackedLinear, rank: int, world: int) -> HybridPackedLi
 
 
 class AllReduceLinear(nn.Module):
-    """A K-split shard followed by the all-reduce that completes its output."""
+    """A K-split shard followed by the all-reduce that completes its output.
+
+    ``AllReduceLinear.skip_collective = True`` leaves the collective out (the output is then this
+    rank's partial sum): a measurement aid that attributes decode time to the all-reduces by
+    replaying the same step without them."""
+
+    skip_collective = False
 
     def __init__(self, inner: nn.Module, group=None):
         super().__init__()
@@ -112,6 +118,8 @@ class AllReduceLinear(nn.Module):
 
     def forward(self, x):
         y = self.inner(x)
+        if AllReduceLinear.skip_collective:
+            return y
         if torch.distributed.is_available() and torch.distributed.is_initialized() and \
                 torch.distributed.get_world_size(self.group) > 1:
             torch.distributed.all_reduce(y, group=self.group)

@@ -142,7 +142,8 @@ int qgemv_run_static(const qgemv_problem* p, void* stream);
  * output is not to be trusted.  This call enqueues, on `stream`, a 4-byte copy of the status word
  * into *host_out (host memory; pinned if the copy is to be asynchronous) followed by a reset of
  * the word to 0.  Synchronise the stream before reading *host_out: 0 = every launch since the
- * last query completed normally.  `workspace` is the pointer given to qgemv_run, or NULL for the
+ * last query completed normally, 1 = a wait for residual projections ran out, 2 = a wait for an
+ * asynchronous weight copy ran out (never seen; it would mean a lost copy).  `workspace` is the pointer given to qgemv_run, or NULL for the
  * built-in scratch of qgemv_run_static on the current device.  Not capturable in a CUDA graph.
  * It has no counterpart in the reference project (its kernels never wait on each other). */
 int qgemv_workspace_status(const void* workspace, void* stream, int32_t* host_out);

@@ -60,3 +60,61 @@ def test_static_decoder_matches_hf_generate(tiny):
     assert torch.equal(torch.cat([first, rest], 1), ref)
     res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=6, device="cpu", warmups=1)
     assert torch.equal(res["tokens"], ref) and res["generated_tokens"] == 6 and res["decode_tokens_s"] > 0
+
+
+def test_streaming_builder_follows_the_seeded_plan(tiny):
+    """The model built layer by layer from a meta-device skeleton has exactly the planned modules,
+    leaves nothing on the meta device, and under tensor parallelism wraps o_proj / down_proj."""
+    for world in (1, 2):
+        model, plan = mt.build_mixed_model_streaming(tiny, "cpu", world=world, seed=5)
+        ref_plan = mt.seeded_plan(mt.build_fp16_model(tiny, "cpu", world=world), (0.6, 0.3, 0.1), seed=5,
+                                  global_k={"o_proj": 256, "down_proj": 512})
+        assert [(e.name, e.bits, e.outlier_columns) for e in plan] == [(e.name, e.bits, e.outlier_columns) for e in ref_plan]
+        mods = dict(model.named_modules())
+        for e in plan:
+            m = mods[e.name]
+            m = m.inner if isinstance(m, AllReduceLinear) else m
+            want = {2: HybridInt2Linear, 4: HybridInt4Linear, 16: torch.nn.Linear}[e.bits]
+            assert isinstance(m, want), (e.name, type(m))
+            if e.bits != 16:
+                assert m.residual_rank == 8 and m.graph_safe
+        assert not any(t.is_meta for t in list(model.parameters()) + list(model.buffers()))
+        assert sum(isinstance(m, AllReduceLinear) for m in model.modules()) == (4 if world == 2 else 0)
+        assert float(model.model.norm.weight.float().mean()) == 1.0
+        assert float(model.model.rotary_emb.inv_freq[0]) == 1.0
+
+
+def _vocab_shard_rank(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mt.SHAPES["tiny"] = dict(family="llama", layers=2, hidden=256, inter=512, heads=4, kv_heads=2, head_dim=64,
+                                 vocab=320, qkv_bias=False)
+        model = mt.build_fp16_model("tiny", "cpu", seed=3).float()      # the same replica on every rank
+        ids = torch.randint(0, 320, (2, 9), generator=torch.Generator().manual_seed(1))
+        full = StaticGraphDecoder(model, 2, 32, device="cpu")
+        want = torch.cat([full.prefill(ids), full.decode(6)], 1)
+        rows = 320 // world
+        head = torch.nn.Linear(256, rows, bias=False)
+        with torch.no_grad():
+            head.weight.copy_(model.lm_head.weight[rank * rows:(rank + 1) * rows])
+        model.lm_head = head
+        dec = StaticGraphDecoder(model, 2, 32, device="cpu", vocab_shard=(rank, world))
+        got = torch.cat([dec.prefill(ids), dec.decode(6)], 1)
+        ret[rank] = bool(torch.equal(got, want))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocabulary_sharded_greedy_token_two_ranks():
+    """lm_head split by vocabulary rows over two gloo ranks: the exchanged (best logit, index) pairs
+    pick the same tokens as the whole output projection."""
+    import os
+    import torch.multiprocessing as mp
+    port = 31500 + (os.getpid() % 2000)
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_vocab_shard_rank, args=(2, port, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: True, 1: True}
