@@ -19,7 +19,10 @@ MAX_M = 4
 ABI_VERSION = 2
 
 EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_plan_describe", "qgemv_workspace_status", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
-           "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem")
+           "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem",
+           "qcomm_slot_bytes", "qcomm_flag_bytes", "qcomm_state_bytes", "qcomm_allreduce", "qcomm_status", "qcomm_alloc", "qcomm_free",
+           "qcomm_ipc_export", "qcomm_ipc_open", "qcomm_ipc_close")
+COMM_MAX_RANKS, COMM_MAX_BLOCKS, COMM_IPC_HANDLE_BYTES = 8, 64, 64
 
 
 class Problem(C.Structure):
@@ -48,6 +51,12 @@ class PlanInfo(C.Structure):
                 ("inline_projections", C.c_int32), ("ctas_per_sm", C.c_int32), ("stages", C.c_int32),
                 ("run_chunks", C.c_int32), ("runs_per_tile", C.c_int32), ("epilogue_tiles", C.c_int32),
                 ("l2_chunks", C.c_int32), ("projection_parts", C.c_int32), ("chunk_bytes", C.c_int32)]
+
+
+class CommGroup(C.Structure):
+    """``struct qcomm_group`` (include/qcomm_b200.h)."""
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("max_elems", C.c_int32), ("wait_limit", C.c_int32),
+                ("slots", C.c_void_p * COMM_MAX_RANKS), ("flags", C.c_void_p * COMM_MAX_RANKS), ("state", C.c_void_p)]
 
 
 class QgemvError(RuntimeError):
@@ -83,6 +92,26 @@ def lib():
     l.qgemv_plan_describe.restype = C.c_int
     l.qgemv_workspace_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
     l.qgemv_workspace_status.restype = C.c_int
+    l.qcomm_slot_bytes.argtypes = [C.c_int, C.c_int]
+    l.qcomm_slot_bytes.restype = C.c_size_t
+    l.qcomm_flag_bytes.argtypes = [C.c_int]
+    l.qcomm_flag_bytes.restype = C.c_size_t
+    l.qcomm_state_bytes.argtypes = []
+    l.qcomm_state_bytes.restype = C.c_size_t
+    l.qcomm_allreduce.argtypes = [C.POINTER(CommGroup), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    l.qcomm_allreduce.restype = C.c_int
+    l.qcomm_status.argtypes = [C.POINTER(CommGroup), C.c_void_p, C.POINTER(C.c_int32)]
+    l.qcomm_status.restype = C.c_int
+    l.qcomm_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+    l.qcomm_alloc.restype = C.c_int
+    l.qcomm_free.argtypes = [C.c_void_p]
+    l.qcomm_free.restype = C.c_int
+    l.qcomm_ipc_export.argtypes = [C.c_void_p, C.c_void_p]
+    l.qcomm_ipc_export.restype = C.c_int
+    l.qcomm_ipc_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    l.qcomm_ipc_open.restype = C.c_int
+    l.qcomm_ipc_close.argtypes = [C.c_void_p]
+    l.qcomm_ipc_close.restype = C.c_int
     l.qdequant.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
                            C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     l.qdequant.restype = C.c_int

@@ -20,6 +20,7 @@ UNITS = [
     ("qgemv_api.cu", [], "qgemv_api.o"),
     ("qgemv_simt.cu", [], "qgemv_simt.o"),
     ("qdequant.cu", [], "qdequant.o"),
+    ("qcomm.cu", [], "qcomm.o"),
     ("qgemv_mma.cu", ["-DQGEMV_INST_BITS=2"], "qgemv_mma_int2.o"),
     ("qgemv_mma.cu", ["-DQGEMV_INST_BITS=4"], "qgemv_mma_int4.o"),
     ("qgemv_pipe.cu", ["-DQGEMV_INST_BITS=2"], "qgemv_pipe_int2.o"),
@@ -44,7 +45,7 @@ def _stale() -> bool:
     if not LIB.exists():
         return True
     t = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "qgemv_b200.h"]
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list((PKG.parent / "include").glob("*.h"))
     return any(d.stat().st_mtime > t for d in deps)
 
 

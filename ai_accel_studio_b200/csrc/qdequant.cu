@@ -7,6 +7,8 @@
 // type, the fp16 scale is converted to the output type, and their product is rounded once.
 // Used for the M > 4 (prefill) path, where the dense matrix feeds a library GEMM, and by the
 // tests that pin "unpacked codes bit-exact".
+#include <type_traits>
+
 #include "qgemv_common.cuh"
 
 namespace qgemv {
@@ -60,6 +62,54 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     }
 }
 
+// One element, rounded exactly as the scalar kernel above does.
+template <int BITS, int DT>
+__device__ __forceinline__ auto dequant_one(int c, __half s16) {
+    if constexpr (DT == QGEMV_F32) {
+        const float lv = BITS == 2 ? level2_f32(c) : float(c - 8);
+        return __fmul_rn(lv, __half2float(s16));
+    } else if constexpr (DT == QGEMV_F16) {
+        const __half lv = BITS == 2 ? level2_f16(c) : __int2half_rn(c - 8);
+        return __float2half_rn(__fmul_rn(__half2float(lv), __half2float(s16)));
+    } else {
+        const float lv = BITS == 2 ? level2_bf16(c) : float(c - 8);
+        const float sb = __bfloat162float(__float2bfloat16_rn(__half2float(s16)));
+        return __float2bfloat16_rn(__fmul_rn(lv, sb));
+    }
+}
+
+// Vector path: a thread turns one aligned 32-bit word of codes (8 INT4 or 16 INT2 weights) into 16-byte
+// stores; consecutive threads take consecutive words, so loads and stores are fully coalesced.
+// Needs 4-byte aligned packed rows, 16-byte aligned output rows, and K and the group size multiples of
+// the weights per word (a word then never straddles a group or the end of a row).
+template <int BITS, int DT>
+__global__ void __launch_bounds__(256) dequant_vec_kernel(const uint8_t* __restrict__ packed, long long ldp,
+                                                          const __half* __restrict__ scales, long long lds,
+                                                          int n, int korig, int group, void* __restrict__ out,
+                                                          long long ldo) {
+    constexpr int WPW = 32 / BITS;                                    // weights per word
+    using OT = std::conditional_t<DT == QGEMV_F32, float, std::conditional_t<DT == QGEMV_F16, __half, __nv_bfloat16>>;
+    constexpr int VEC = 16 / (int)sizeof(OT);                         // elements per 16-byte store
+    const int words_per_row = korig / WPW;
+    const long long total = (long long)n * words_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / words_per_row), wi = (int)(i - (long long)row * words_per_row);
+        const uint32_t word = *reinterpret_cast<const uint32_t*>(packed + (size_t)row * ldp + (size_t)wi * 4);
+        const int kbase = wi * WPW;
+        const __half s16 = scales[(size_t)row * lds + kbase / group];
+        OT* o = static_cast<OT*>(out) + (size_t)row * ldo + kbase;
+#pragma unroll
+        for (int v = 0; v < WPW / VEC; ++v) {
+            __align__(16) OT vals[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                vals[j] = dequant_one<BITS, DT>((int)((word >> (BITS * (v * VEC + j))) & ((1u << BITS) - 1u)), s16);
+            *reinterpret_cast<uint4*>(o + v * VEC) = *reinterpret_cast<const uint4*>(vals);
+        }
+    }
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(256) unpack_codes_kernel(const uint8_t* __restrict__ packed, long long ldp,
                                                            int n, int kpad, uint8_t* __restrict__ codes,
@@ -105,11 +155,18 @@ extern "C" int qdequant(int bits, const uint8_t* packed, int64_t ldp, const void
         return QGEMV_ERR_SHAPE;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int cpb = 8 / bits;
-    const long long total = (long long)n * ((k_original + cpb - 1) / cpb);
+    const int cpb = 8 / bits, wpw = 32 / bits;
+    const size_t esize = out_dtype == QGEMV_F32 ? 4 : 2;
+    const bool vec = reinterpret_cast<uintptr_t>(packed) % 4 == 0 && ldp % 4 == 0 && k_original % wpw == 0 && group % wpw == 0 &&
+                     reinterpret_cast<uintptr_t>(out) % 16 == 0 && (ld_out * esize) % 16 == 0;
+    const long long total = vec ? (long long)n * (k_original / wpw) : (long long)n * ((k_original + cpb - 1) / cpb);
     const int grid = grid_for(total);
     const __half* sc = static_cast<const __half*>(scales);
-#define QD_LAUNCH(B, D) dequant_kernel<B, D><<<grid, 256, 0, s>>>(packed, ldp, sc, lds, n, k_original, group, out, ld_out)
+#define QD_LAUNCH(B, D)                                                                                              \
+    do {                                                                                                             \
+        if (vec) dequant_vec_kernel<B, D><<<grid, 256, 0, s>>>(packed, ldp, sc, lds, n, k_original, group, out, ld_out); \
+        else dequant_kernel<B, D><<<grid, 256, 0, s>>>(packed, ldp, sc, lds, n, k_original, group, out, ld_out);     \
+    } while (0)
     if (bits == 2) {
         if (out_dtype == QGEMV_F32) QD_LAUNCH(2, QGEMV_F32);
         else if (out_dtype == QGEMV_F16) QD_LAUNCH(2, QGEMV_F16);

@@ -38,6 +38,7 @@ struct MmaArgs {
     int off_cnt;       // per-tile arrival counters of the CTA, followed by the "table of t is ready" flag
     int off_red;       // per-warp partial sums of a residual-projection job
     int off_bar;       // mbarriers: one per ring slot per warp, then one for the epilogue operands
+    int tma3d;         // 1: one 3-D box per ring slot; 0: one 2-D box per group of the chunk
 };
 
 namespace {

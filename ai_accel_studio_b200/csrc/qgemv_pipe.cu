@@ -14,14 +14,16 @@
 //    of its share to L2) BEFORE griddepcontrol.wait.  While launch n computes, launch n+1 already
 //    has ~60 KB per SM of its weights on chip or in flight: DRAM keeps streaming through the
 //    prologue and the tail of every launch, which is where the phased kernel left it idle.
-//  * The ring is filled by the bulk-copy engine (cp.async.bulk global -> shared, one copy per row per
-//    slot, completion counted in bytes on an mbarrier per slot), not by per-thread cp.async.  With two
-//    CTAs on an SM, the waiting CTA's 16-byte copies sat in the load/store queues that the running
-//    CTA's shared-memory loads also go through, and stalled them (measured with cp.async: the main
-//    loop of the running launch took 14 us instead of 3, a dependent 8-byte load 3 us).  A bulk copy
-//    is one instruction for a whole row and its traffic never enters those queues.  Bulk copies
-//    write contiguous bytes, so the bank-conflict-free layout is a per-row ROTATION (row r starts
-//    (r mod R) * 128/R bytes into its slot row, written as two copies) instead of an XOR swizzle.
+//  * The ring is filled by the tensor-map copy engine (TMA): ONE request per slot for the codes (a
+//    16-row x CB-byte box) and one for the scales, completion counted in bytes on an mbarrier per slot.
+//    Two other ways were measured first.  Per-thread 16-byte cp.async copies: with two CTAs on an SM
+//    the waiting CTA's copies sit in the load/store queues that the running CTA's shared-memory loads
+//    also go through; the running launch's main loop took 14 us instead of 3 and a dependent 8-byte
+//    load 3 us.  One bulk copy per row per slot (40 requests per 4 KB slot): the copy engine handles
+//    roughly one request per ten cycles, so the requests, not the bytes, set the pace (23 us per GEMV).
+//    The packed matrix is described to the engine as a 3-D tensor [group bytes][row][group], so the box
+//    lands in shared memory as [group][row][group bytes]: the lanes of one shared-memory load then read
+//    128 contiguous bytes, and no swizzle is needed.
 //  * After the wait only x-dependent work is left: load x (L2 hits), stage it in B-fragment order,
 //    gather the outlier activations, one CTA barrier, main loop.
 //  * No barrier after the main loop.  A warp that completes a run parks its partial sums and bumps
@@ -38,13 +40,27 @@
 //
 // Replaces _decode_gemv (ai_accel_lab/kernels/decode_int2.py:43-96) and _decode_int4_gemv
 // (ai_accel_lab/kernels/groupwise_int4.py:85-107) of the reference project.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "qgemv_mma_dev.cuh"
 
 namespace qgemv {
+
+// Tensor maps of one launch (kernel parameter): packed codes, scales, outlier weights, residual rows.
+struct PipeMaps {
+    CUtensorMap w, s, ow, ru;
+};
+
 namespace {
 
 constexpr int kPipeWarps = 8;                 // warps per CTA the kernel is compiled for (128 registers x 256 threads x 2 CTAs = one SM)
 constexpr int kPipeMaxStages = 8;             // ring descriptors reserved per warp
+#ifndef QGEMV_BATCH_GROUPS
+#define QGEMV_BATCH_GROUPS 4
+#endif
+constexpr int kBatchGroups = QGEMV_BATCH_GROUPS;   // groups whose tensor-core chains a warp keeps in flight together
 constexpr int kSmemPerSm = 233472;            // 228 KB of shared memory per SM on sm_100
 constexpr int kHalfSmSmem = (kSmemPerSm - 2 * 1024) / 2;   // dynamic bytes that let two CTAs share an SM (1 KB per CTA is reserved)
 constexpr int kBarSpinLimit = 1 << 22;        // bound of the wait for a bulk copy (each probe blocks for a while in hardware)
@@ -66,8 +82,18 @@ constexpr int kTagSpinLimitDebug = 1 << 7;    // ... with QGEMV_DEBUG_DROP_PROJE
                   (size_t)blockIdx.x * kPipeWarps + (threadIdx.x >> 5)) * 16 + (slot)] = t_;    \
         }                                                                                       \
     } while (0)
+#define PTRACE_VAL(slot, value)                                                                 \
+    do {                                                                                        \
+        if ((threadIdx.x & 31) == 0)                                                            \
+            reinterpret_cast<unsigned long long*>(p.a.partial + (kMaxPartialFloats / 2))        \
+                [((size_t)((p.debug >> 24) & 15) * 148 * kPipeWarps +                           \
+                  (size_t)blockIdx.x * kPipeWarps + (threadIdx.x >> 5)) * 16 + (slot)] = (value); \
+    } while (0)
+#define PTRACE_NOW(var) unsigned long long var; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(var) :: "memory")
 #else
 #define PTRACE(slot) do { } while (0)
+#define PTRACE_VAL(slot, value) do { } while (0)
+#define PTRACE_NOW(var) do { } while (0)
 #endif
 
 // Announce `bytes` (multiple of 16) at a 16-byte aligned global address to L2; no data reaches the SM.
@@ -95,6 +121,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// Tiled tensor-map copies of one box into this CTA's shared memory (128-byte aligned), completion on `bar`.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(c0), "r"(c1) : "memory");
 }
 // Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy ones.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -342,7 +383,8 @@ __device__ __noinline__ void pipe_build_t_table(const MmaArgs& p, unsigned char*
 // and consumer of a ring of asynchronous copies.
 // ---------------------------------------------------------------------------------------------
 template <int BITS, int GB, int CB, int M, bool BF16, bool EX>
-__global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __grid_constant__ MmaArgs p) {
+__global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __grid_constant__ MmaArgs p,
+                                                                         const __grid_constant__ PipeMaps tm) {
     using GE = Geo<BITS, GB, CB>;
     constexpr int TT = (M + 1) / 2;                   // quad lanes that hold useful output columns
     constexpr int SLOT_BYTES = 8 * TT * 16;           // one run's partial sums in shared memory
@@ -383,6 +425,7 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     }
     fence_proxy_async();
     __syncthreads();                                 // barriers and counters initialised before any copy can signal them
+    PTRACE(1);
 
     // ---- producer side --------------------------------------------------------------------------
     const bool t_inline = EX && p.t_inline;
@@ -398,16 +441,9 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     } else {
         pf_run = -1;
     }
-    // A slot holds 16 rows of CB packed bytes, each rotated by ROT(row) bytes inside its CB-byte
-    // slot row, followed by 16 bytes of scales per row: the 8 scales of the aligned block of 8 groups
-    // that contains the chunk's groups.  Copy items of one slot: item i < 16 is row i from its
-    // rotation point to the end of the slot row, 16 <= i < 32 the part of row i - 16 that wraps to the
-    // start, 32 <= i < 48 the scale block of row i - 32.  Lane l issues items l and l + 32.
-    constexpr int ROT_ROWS = GE::SWZ_ROWS, ROT_STEP = 128 / GE::SWZ_ROWS;   // row r starts (r % ROT_ROWS) * ROT_STEP bytes in
-    const int crow = lane & 15;                       // row of this lane's code item and of its scale item
-    const int crot = (crow % ROT_ROWS) * ROT_STEP;
-    const bool wraps = lane >= 16;                    // this lane's code item is the wrapped part
-    const bool ragged_n = (a.n % kTileRows) != 0;
+    // A slot holds the codes of one chunk as [group][row][GB bytes] (16 rows, CG groups), followed by
+    // 16 bytes of scales per row: the 8 scales of the aligned block of 8 groups that contains the
+    // chunk's groups.  Rows past N and groups past the end of a row are zero-filled by the engine.
     // Step the (run, chunk) cursor of this warp to the next chunk it owns; false when there is none.
     auto advance = [&]() {
         if (pf_run >= 0 && pf_ch == pf_end) {          // current run exhausted: step to this warp's next run
@@ -426,26 +462,23 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     auto issue_next = [&](int s) {
         if (advance()) {
             const int ngr = min(GE::CG, p.ng - pf_ch * GE::CG);
-            const int len = ngr * GB;                                  // packed bytes per row of this chunk
             const uint32_t sbase = ring_u32 + s * GE::STAGE_BYTES;
             const uint32_t bar = bars_u32 + s * 8;
-            // rows past N (last, ragged tile) repeat the last row; their results are never stored
-            const int row = ragged_n ? min(pf_tile * kTileRows + crow, a.n - 1) : pf_tile * kTileRows + crow;
+            const int row0 = pf_tile * kTileRows, g0 = pf_ch * GE::CG;
             fence_proxy_async();                                       // this slot was read with ordinary loads a moment ago
-            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(kTileRows * len + (p.scales_async ? kTileRows * 16 : 0)));
-            __syncwarp();
-            {
-                const uint8_t* src = a.packed + (size_t)row * a.ldp + (size_t)pf_ch * GE::CB;
-                const int first = min(len, GE::CB - crot);             // bytes from the rotation point to the end of the slot row
-                if (!wraps) bulk_g2s(sbase + crow * GE::PITCH + crot, src, (uint32_t)first, bar);
-                else if (len > first) bulk_g2s(sbase + crow * GE::PITCH, src + first, (uint32_t)(len - first), bar);
+            if (lane == 0) {
+                const int code_bytes = p.tma3d ? kTileRows * GE::CB : kTileRows * GB * ngr;
+                mbar_arrive_expect_tx(bar, (uint32_t)(code_bytes + (p.scales_async ? kTileRows * 16 : 0)));
+                if (p.tma3d) tma_load_3d(sbase, &tm.w, 0, row0, g0, bar);
+                if (p.scales_async) tma_load_2d(sbase + GE::SCALE_OFF, &tm.s, g0 & ~7, row0, bar);
             }
-            if (p.scales_async) {
-                if (lane < kTileRows)
-                    bulk_g2s(sbase + GE::SCALE_OFF + lane * 16, a.scales + (size_t)row * a.lds + ((pf_ch * GE::CG) & ~7), 16u, bar);
-            } else if (lane < kTileRows) {                             // unaligned scale rows: plain loads, this row's groups of the chunk
-                const __half* src = a.scales + (size_t)row * a.lds + pf_ch * GE::CG;
-                __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16) + ((pf_ch * GE::CG) & 7);
+            __syncwarp();
+            if (!p.tma3d && lane < ngr)                                // one 16-row x GB box per group of the chunk
+                tma_load_2d(sbase + lane * (kTileRows * GB), &tm.w, (g0 + lane) * GB, row0, bar);
+            if (!p.scales_async && lane < kTileRows) {                 // unaligned scale rows: plain loads, this row's groups of the chunk
+                const int row = min(row0 + lane, a.n - 1);
+                const __half* src = a.scales + (size_t)row * a.lds + g0;
+                __half* d = reinterpret_cast<__half*>(ring + s * GE::STAGE_BYTES + GE::SCALE_OFF + lane * 16) + (g0 & 7);
                 for (int i = 0; i < ngr; ++i) d[i] = __ldg(src + i);
             }
             if (lane == 0) meta[s] = make_int4(pf_tile, pf_ch, pf_run - r0, pf_ch + 1 == pf_end);
@@ -456,8 +489,8 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     };
 
     // ---- everything that does not depend on the previous kernel -----------------------------------
-    // Epilogue operands (outlier-weight rows, residual rows, bias) of the CTA's first tiles: one bulk
-    // copy per row, all counted on one barrier that every thread checks before the prologue ends.
+    // Epilogue operands (outlier-weight rows, residual rows, bias) of the CTA's first tiles: one box
+    // each per tile, all counted on one barrier that every thread checks before the prologue ends.
     {
         const int full_tiles = a.n / kTileRows;                       // tiles that lie completely inside N
         const int npre = p.epi_async ? min(min(p.epi_tiles, ntl), max(0, full_tiles - T0)) : 0;
@@ -465,30 +498,27 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
         if (tid == 0) mbar_arrive_expect_tx(epi_bar, (uint32_t)(npre * (kTileRows * (ocb + rb) + bb)));
         __syncwarp();
         const uint32_t epi_u32 = smem_u32(smem + p.off_epi);
-        const int per_tile = 2 * kTileRows + 1;                       // items: 16 outlier rows, 16 residual rows, bias
-        for (int i = tid; i < npre * per_tile; i += blockDim.x) {
-            const int lt = i / per_tile, q = i - lt * per_tile;
+        for (int i = tid; i < npre * 3; i += blockDim.x) {
+            const int lt = i / 3, q = i - lt * 3;
             const int row0 = (T0 + lt) * kTileRows;
             const uint32_t dst = epi_u32 + lt * p.epi_bytes;
-            if (q < kTileRows) {
-                if (ocb) bulk_g2s(dst + q * ocb, a.ow + (size_t)(row0 + q) * a.ldow, (uint32_t)ocb, epi_bar);
-            } else if (q < 2 * kTileRows) {
-                const int r = q - kTileRows;
-                if (rb) bulk_g2s(dst + kTileRows * ocb + r * rb, a.ru + (size_t)(row0 + r) * a.ldu, (uint32_t)rb, epi_bar);
-            } else if (bb) {
-                bulk_g2s(dst + kTileRows * (ocb + rb), a.bias + row0, 32u, epi_bar);
-            }
+            if (q == 0) { if (ocb) tma_load_2d(dst, &tm.ow, 0, row0, epi_bar); }
+            else if (q == 1) { if (rb) tma_load_2d(dst + kTileRows * ocb, &tm.ru, 0, row0, epi_bar); }
+            else if (bb) bulk_g2s(dst + kTileRows * (ocb + rb), a.bias + row0, 32u, epi_bar);
         }
     }
+    PTRACE(6);
     for (int s = 0; s < nstages; ++s) issue_next(s);
-    // The chunks that follow the ring go to L2 now (one instruction per chunk: lanes 0..15 take a row
-    // each), so that the main loop finds them there instead of in DRAM.
-    if (p.l2_chunks > 0 && lane < kTileRows) {
+    PTRACE(7);
+    // The chunks that follow the ring are announced to L2 now (one request per chunk), so that the main
+    // loop finds them there instead of in DRAM.
+    if (p.l2_chunks > 0 && lane == 0) {
         const int s_run = pf_run, s_tile = pf_tile, s_j = pf_j, s_ch = pf_ch, s_end = pf_end;
         for (int i = 0; i < p.l2_chunks && advance(); ++i) {
-            const int row = pf_tile * kTileRows + lane;
-            const int ngr = min(GE::CG, p.ng - pf_ch * GE::CG);
-            if (row < a.n) l2_prefetch_bulk(a.packed + (size_t)row * a.ldp + (size_t)pf_ch * GE::CB, (uint32_t)(ngr * GB));
+            if (p.tma3d) tma_prefetch_3d(&tm.w, 0, pf_tile * kTileRows, pf_ch * GE::CG);
+            else
+                for (int gi = 0; gi < min(GE::CG, p.ng - pf_ch * GE::CG); ++gi)
+                    tma_prefetch_2d(&tm.w, (pf_ch * GE::CG + gi) * GB, pf_tile * kTileRows);
             ++pf_ch;
         }
         pf_run = s_run; pf_tile = s_tile; pf_j = s_j; pf_ch = s_ch; pf_end = s_end;
@@ -513,6 +543,7 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     unsigned t_tag = 0;
     if (t_inline && (warp == 0 || t_reader)) t_tag = ld_relaxed_u32(a.counters + kWsEpochIdx) + 1u;
     pipe_stage_x<BITS, GB, M, BF16, EX>(p, smem, cols);
+    PTRACE(10);
     {                                                 // the epilogue operands have landed (long ago, normally)
         int spins = 0;
         while (!mbar_try_wait(epi_bar, 0)) {
@@ -544,16 +575,14 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     const uint32_t gx_a_u32 = smem_u32(smem + p.off_gx) + ma * 8, gx_b_u32 = smem_u32(smem + p.off_gx) + mb * 8;
     const uint32_t slots_u32 = smem_u32(slots) + (g * TT + t) * 16;
     const uint32_t meta_u32 = smem_u32(meta);
-    const int rot = (g % ROT_ROWS) * ROT_STEP;                      // rotation of rows g and g + 8 inside their slot rows
-    const uint32_t lane_row_u32 = ring_u32 + g * GE::PITCH;         // row g of slot 0 (row g+8 is 8 rows further)
+    const uint32_t lane_row_u32 = ring_u32 + g * GB + t * GE::TB;   // this lane's bytes of row g, group 0, slot 0 (row g+8: 8 rows further)
     const uint32_t lane_sc_u32 = ring_u32 + GE::SCALE_OFF + g * 16;
     const int ng_total = p.ng;
     constexpr int GSTRIDE = GE::TW * (GE::NCLS / 2) * M * 4 * 16;    // bytes of staged x per group
 
     // One group of one chunk: G = absolute group index, gi = group inside the chunk.
     auto do_group = [&](uint32_t rowa, uint32_t rowb, int gi, int G, float s0, float s1, float (&yy)[4]) {
-        const int lo = gi * GB + t * GE::TB;                          // logical byte offset of this lane's bytes
-        const uint32_t off = (uint32_t)((lo + rot) & (GE::CB - 1));   // rotations are multiples of 4 * TB: a lane's bytes never wrap
+        const uint32_t off = (uint32_t)(gi * (kTileRows * GB));       // groups are kTileRows * GB bytes apart in a slot
         uint32_t w0[GE::TW], w1[GE::TW];
         if constexpr (GE::TW == 1) {
             w0[0] = lds32(rowa + off); w1[0] = lds32(rowb + off);
@@ -602,6 +631,71 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
         yy[3] = fmaf(s1, fmaf(gb.y, accA[3] + accB[3], -gb.x), yy[3]);
     };
 
+    // NB consecutive groups of one chunk, starting at group gi0 of the chunk (absolute group G0 + gi0),
+    // with the tensor-core instructions of the NB groups interleaved step by step.  A warp's
+    // mma.sync instructions on one accumulator are a dependent chain, and the legacy tensor path has
+    // a long latency on this part: group after group (do_group) a warp needs ~600 cycles per group
+    // and the kernel is bound by that latency, whatever the number of resident warps (measured: the same
+    // 1.2 us per 4 KB chunk per warp with 7 and with 16 warps per SM).  Interleaving keeps 2 * NB
+    // independent chains in flight per warp.  Same arithmetic, same order per group as do_group.
+    auto do_batch = [&](auto nb_tag, uint32_t rowa, uint32_t rowb, int gi0, int G0, const __half* sc0, const __half* sc1,
+                        float (&yy)[4]) {
+        constexpr int NB = decltype(nb_tag)::value;
+        uint32_t w0[NB][GE::TW], w1[NB][GE::TW];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) {
+            const uint32_t off = (uint32_t)((gi0 + n) * (kTileRows * GB));
+            if constexpr (GE::TW == 1) {
+                w0[n][0] = lds32(rowa + off); w1[n][0] = lds32(rowb + off);
+            } else if constexpr (GE::TW == 2) {
+                const uint2 v0 = lds64(rowa + off), v1 = lds64(rowb + off);
+                w0[n][0] = v0.x; w0[n][1] = v0.y; w1[n][0] = v1.x; w1[n][1] = v1.y;
+            } else {
+                const uint4 v0 = lds128(rowa + off), v1 = lds128(rowb + off);
+                w0[n][0] = v0.x; w0[n][1] = v0.y; w0[n][2] = v0.z; w0[n][3] = v0.w;
+                w1[n][0] = v1.x; w1[n][1] = v1.y; w1[n][2] = v1.z; w1[n][3] = v1.w;
+            }
+        }
+        const uint32_t xg = xs_lane_u32 + (uint32_t)(G0 + gi0) * GSTRIDE;
+        float accA[NB][4], accB[NB][4];
+#pragma unroll
+        for (int i = 0; i < GE::TW; ++i) {
+#pragma unroll
+            for (int cp = 0; cp < GE::NCLS / 2; ++cp) {
+                constexpr uint32_t MK = GE::MASK;
+                const uint32_t m0 = MK << (BITS * (2 * cp)), m1 = MK << (BITS * (2 * cp + 1));
+#pragma unroll
+                for (int n = 0; n < NB; ++n) {
+                    const uint4 bb = lds128(xg + (uint32_t)n * GSTRIDE + (i * (GE::NCLS / 2) + cp) * (M * 4 * 16));
+                    const uint32_t a0 = w0[n][i], a1 = w1[n][i], h0 = a0 >> 8, h1 = a1 >> 8;
+                    if (i == 0 && cp == 0) {
+                        mma_f16_first(accA[n], a0 & m0, a1 & m0, h0 & m0, h1 & m0, bb.x, bb.y);
+                        mma_f16_first(accB[n], a0 & m1, a1 & m1, h0 & m1, h1 & m1, bb.z, bb.w);
+                    } else {
+                        mma_f16(accA[n], a0 & m0, a1 & m0, h0 & m0, h1 & m0, bb.x, bb.y);
+                        mma_f16(accB[n], a0 & m1, a1 & m1, h0 & m1, h1 & m1, bb.z, bb.w);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NB; ++n) {
+            const int G = G0 + gi0 + n;
+            float2 ga, gb;
+            if constexpr (M % 2 == 0) {
+                const float4 gq = lds128f(gx_lane_u32 + (uint32_t)G * (M * 8));
+                ga = make_float2(gq.x, gq.y); gb = make_float2(gq.z, gq.w);
+            } else {
+                ga = lds64f(gx_a_u32 + (uint32_t)G * (M * 8)); gb = lds64f(gx_b_u32 + (uint32_t)G * (M * 8));
+            }
+            const float s0 = __half2float(sc0[gi0 + n]), s1 = __half2float(sc1[gi0 + n]);
+            yy[0] = fmaf(s0, fmaf(ga.y, accA[n][0] + accB[n][0], -ga.x), yy[0]);
+            yy[1] = fmaf(s0, fmaf(gb.y, accA[n][1] + accB[n][1], -gb.x), yy[1]);
+            yy[2] = fmaf(s1, fmaf(ga.y, accA[n][2] + accB[n][2], -ga.x), yy[2]);
+            yy[3] = fmaf(s1, fmaf(gb.y, accA[n][3] + accB[n][3], -gb.x), yy[3]);
+        }
+    };
+
     // Residual projections computed by other CTAs: the reader warp requests a small table now (the
     // producers publish right after their own barrier) and checks the tags one ring slot later.
     const int t_entries = t_inline ? p.t_parts * a.rank * M : 0;
@@ -627,21 +721,29 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
     int stage = 0;
     uint32_t phases = 0;                            // bit s: parity of the next completion of slot s's barrier
     bool first = true;
+#ifdef QGEMV_TRACE
+    unsigned long long waited_ns = 0, epilogue_ns = 0, iterations = 0;
+#endif
     for (;;) {
         __syncwarp();                               // lane 0's descriptor of this slot is visible
         const uint4 mt = lds128(meta_u32 + stage * 16);          // tile, chunk, slot, last-of-run
         if ((int)mt.x < 0) break;
         {                                           // the slot's bytes have landed
+            PTRACE_NOW(w0_);
             const uint32_t bar = bars_u32 + stage * 8, parity = (phases >> stage) & 1u;
             int spins = 0;
             while (!mbar_try_wait(bar, parity)) {
                 if (++spins > kBarSpinLimit) { atomicExch(a.counters + kWsStatusIdx, 2); break; }
             }
             phases ^= 1u << stage;
+#ifdef QGEMV_TRACE
+            PTRACE_NOW(w1_);
+            waited_ns += w1_ - w0_; ++iterations;
+#endif
         }
         if (first) { PTRACE(3); first = false; }
         const int ch = (int)mt.y;
-        const uint32_t rowa = lane_row_u32 + stage * GE::STAGE_BYTES, rowb = rowa + 8 * GE::PITCH;
+        const uint32_t rowa = lane_row_u32 + stage * GE::STAGE_BYTES, rowb = rowa + 8 * GB;
         const uint32_t sca = lane_sc_u32 + stage * GE::STAGE_BYTES + (((uint32_t)ch * GE::CG) & 7u) * 2, scb = sca + 8 * 16;
         __align__(16) __half sc0[8], sc1[8];
         if constexpr (GE::CG == 8) {
@@ -652,10 +754,11 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
             *reinterpret_cast<uint32_t*>(sc0) = lds32(sca); *reinterpret_cast<uint32_t*>(sc1) = lds32(scb);
         }
         const int G0 = ch * GE::CG;
-        if (G0 + GE::CG <= ng_total) {             // full chunk: straight-line code
+        if (G0 + GE::CG <= ng_total) {             // full chunk: straight-line code, groups interleaved in batches
+            constexpr int NB = GE::CG < kBatchGroups ? GE::CG : kBatchGroups;
 #pragma unroll
-            for (int gi = 0; gi < GE::CG; ++gi)
-                do_group(rowa, rowb, gi, G0 + gi, __half2float(sc0[gi]), __half2float(sc1[gi]), y);
+            for (int gi0 = 0; gi0 < GE::CG; gi0 += NB)
+                do_batch(std::integral_constant<int, NB>{}, rowa, rowb, gi0, G0, sc0, sc1, y);
         } else {                                   // last, shorter chunk of a row
 #pragma unroll
             for (int gi = 0; gi < GE::CG; ++gi)
@@ -675,6 +778,7 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
             if (lane == 0) { __threadfence_block(); old = atomicAdd(cnt + lt, 1); }
             old = __shfl_sync(0xffffffffu, old, 0);
             if (old == p.rpt - 1) {                 // last run of the tile: add the runs in run order and finish it
+                PTRACE_NOW(e0_);
                 __threadfence_block();
                 float yy[4] = {0.f, 0.f, 0.f, 0.f};
                 if (t < TT) {
@@ -695,11 +799,18 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
                 PTRACE(14);
                 const bool pre = p.epi_async && lt < p.epi_tiles && (tile + 1) * kTileRows <= a.n;
                 finish_tile<M, BF16, EX>(p, smem, tile, yy, pre ? smem + p.off_epi + (size_t)lt * p.epi_bytes : nullptr);
+#ifdef QGEMV_TRACE
+                PTRACE_NOW(e1_);
+                epilogue_ns += e1_ - e0_;
+#endif
             }
         }
     }
     if (t_pending) publish_table();                 // a reader warp without work still owes the table
     PTRACE(5);
+#ifdef QGEMV_TRACE
+    PTRACE_VAL(11, waited_ns); PTRACE_VAL(13, iterations); PTRACE_VAL(15, epilogue_ns);
+#endif
     if (t_inline && a.rank > 0 && tid == 0) {
         // The last CTA to get here advances the launch count (every CTA has read it, and every reader
         // has its projections) and clears the arrival counter for the next launch.
@@ -712,7 +823,7 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 2) qgemv_pipe_kernel(const __
 }
 
 template <int BITS, int GB, int CB, int M, bool BF16, bool EX>
-int pipe_launch_ex(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
+int pipe_launch_ex(const MmaArgs& p, const PipeMaps& tm, int grid, int smem_bytes, cudaStream_t s) {
     auto kern = qgemv_pipe_kernel<BITS, GB, CB, M, BF16, EX>;
     static bool configured[64] = {false};
     int dev = 0;
@@ -738,33 +849,33 @@ int pipe_launch_ex(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) return check_launch("qgemv_pipe_kernel");
+    if (cudaLaunchKernelEx(&cfg, kern, p, tm) != cudaSuccess) return check_launch("qgemv_pipe_kernel");
     return check_launch("qgemv_pipe_kernel");
 }
 
 template <int BITS, int GB, int CB, int M, bool BF16>
-int pipe_launch_one(const MmaArgs& p, int grid, int smem_bytes, cudaStream_t s) {
-    if (p.a.oc > 0 || p.a.rank > 0) return pipe_launch_ex<BITS, GB, CB, M, BF16, true>(p, grid, smem_bytes, s);
-    return pipe_launch_ex<BITS, GB, CB, M, BF16, false>(p, grid, smem_bytes, s);
+int pipe_launch_one(const MmaArgs& p, const PipeMaps& tm, int grid, int smem_bytes, cudaStream_t s) {
+    if (p.a.oc > 0 || p.a.rank > 0) return pipe_launch_ex<BITS, GB, CB, M, BF16, true>(p, tm, grid, smem_bytes, s);
+    return pipe_launch_ex<BITS, GB, CB, M, BF16, false>(p, tm, grid, smem_bytes, s);
 }
 template <int BITS, int GB, int CB, int M>
-int pipe_launch_bf(const MmaArgs& p, bool bf16, int grid, int smem, cudaStream_t s) {
-    return bf16 ? pipe_launch_one<BITS, GB, CB, M, true>(p, grid, smem, s) : pipe_launch_one<BITS, GB, CB, M, false>(p, grid, smem, s);
+int pipe_launch_bf(const MmaArgs& p, const PipeMaps& tm, bool bf16, int grid, int smem, cudaStream_t s) {
+    return bf16 ? pipe_launch_one<BITS, GB, CB, M, true>(p, tm, grid, smem, s) : pipe_launch_one<BITS, GB, CB, M, false>(p, tm, grid, smem, s);
 }
 template <int BITS, int GB, int CB>
-int pipe_launch_m(const MmaArgs& p, bool bf16, int grid, int smem, cudaStream_t s) {
+int pipe_launch_m(const MmaArgs& p, const PipeMaps& tm, bool bf16, int grid, int smem, cudaStream_t s) {
     switch (p.a.m) {
-        case 1: return pipe_launch_bf<BITS, GB, CB, 1>(p, bf16, grid, smem, s);
-        case 2: return pipe_launch_bf<BITS, GB, CB, 2>(p, bf16, grid, smem, s);
-        case 3: return pipe_launch_bf<BITS, GB, CB, 3>(p, bf16, grid, smem, s);
-        default: return pipe_launch_bf<BITS, GB, CB, 4>(p, bf16, grid, smem, s);
+        case 1: return pipe_launch_bf<BITS, GB, CB, 1>(p, tm, bf16, grid, smem, s);
+        case 2: return pipe_launch_bf<BITS, GB, CB, 2>(p, tm, bf16, grid, smem, s);
+        case 3: return pipe_launch_bf<BITS, GB, CB, 3>(p, tm, bf16, grid, smem, s);
+        default: return pipe_launch_bf<BITS, GB, CB, 4>(p, tm, bf16, grid, smem, s);
     }
 }
 template <int BITS>
-int pipe_launch_gb(const MmaArgs& p, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s) {
-    if (gb == 16) return pipe_launch_m<BITS, 16, 128>(p, bf16, grid, smem, s);
-    if (gb == 32) return cb == 128 ? pipe_launch_m<BITS, 32, 128>(p, bf16, grid, smem, s) : pipe_launch_m<BITS, 32, 256>(p, bf16, grid, smem, s);
-    return cb == 128 ? pipe_launch_m<BITS, 64, 128>(p, bf16, grid, smem, s) : pipe_launch_m<BITS, 64, 256>(p, bf16, grid, smem, s);
+int pipe_launch_gb(const MmaArgs& p, const PipeMaps& tm, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s) {
+    if (gb == 16) return pipe_launch_m<BITS, 16, 128>(p, tm, bf16, grid, smem, s);
+    if (gb == 32) return cb == 128 ? pipe_launch_m<BITS, 32, 128>(p, tm, bf16, grid, smem, s) : pipe_launch_m<BITS, 32, 256>(p, tm, bf16, grid, smem, s);
+    return cb == 128 ? pipe_launch_m<BITS, 64, 128>(p, tm, bf16, grid, smem, s) : pipe_launch_m<BITS, 64, 256>(p, tm, bf16, grid, smem, s);
 }
 
 }  // namespace
@@ -772,13 +883,13 @@ int pipe_launch_gb(const MmaArgs& p, int gb, int cb, bool bf16, int grid, int sm
 // One translation unit per bit width keeps the build parallel: QGEMV_INST_BITS selects which
 // instantiations (and, for 2, the planner) this compilation provides.
 #if !defined(QGEMV_INST_BITS) || QGEMV_INST_BITS == 2
-int launch_pipe_int2(const MmaArgs& p, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s) {
-    return pipe_launch_gb<2>(p, gb, cb, bf16, grid, smem, s);
+int launch_pipe_int2(const MmaArgs& p, const PipeMaps& tm, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s) {
+    return pipe_launch_gb<2>(p, tm, gb, cb, bf16, grid, smem, s);
 }
 #endif
 #if !defined(QGEMV_INST_BITS) || QGEMV_INST_BITS == 4
-int launch_pipe_int4(const MmaArgs& p, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s) {
-    return pipe_launch_gb<4>(p, gb, cb, bf16, grid, smem, s);
+int launch_pipe_int4(const MmaArgs& p, const PipeMaps& tm, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s) {
+    return pipe_launch_gb<4>(p, tm, gb, cb, bf16, grid, smem, s);
 }
 #endif
 
@@ -799,8 +910,8 @@ MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base) {
     pl.nch = (pl.ng + cg - 1) / cg;
     {
         auto al0 = [](const void* q, size_t a) { return reinterpret_cast<uintptr_t>(q) % a == 0; };
-        // scale rows go through the bulk-copy engine in aligned blocks of 8 scales (16 bytes)
-        pl.scales_async = (p.lds % 8 == 0) && (pl.ng % 8 == 0) && al0(p.scales, 16) ? 1 : 0;
+        // scale rows go through the copy engine in aligned blocks of 8 scales (16 bytes; zero fill past the row's end)
+        pl.scales_async = (p.lds % 8 == 0) && al0(p.scales, 16) ? 1 : 0;
     }
     const int sms = sm_count();
     const int grid = pl.nt < sms ? pl.nt : sms;
@@ -822,7 +933,8 @@ MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base) {
     nw_cap = nw_cap < 1 ? 1 : (nw_cap > kPipeWarps ? kPipeWarps : nw_cap);
 
     // epilogue operands: prefetched for the first tiles of a CTA, up to 12 KB
-    const int epi_bytes = align_up(kTileRows * (pl.ocb + pl.rb) + 32, 16);
+    // (a tile's operand block is the destination of tensor-map copies: 128-byte aligned)
+    const int epi_bytes = align_up(kTileRows * (pl.ocb + pl.rb) + 32, 128);
     int epi_tiles = 0;
     if (pl.epi_async) {
         epi_tiles = 12288 / epi_bytes;
@@ -890,8 +1002,41 @@ MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base) {
     return pl;
 }
 
-int launch_pipe_int2(const MmaArgs& p, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s);
-int launch_pipe_int4(const MmaArgs& p, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s);
+int launch_pipe_int2(const MmaArgs& p, const PipeMaps& tm, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s);
+int launch_pipe_int4(const MmaArgs& p, const PipeMaps& tm, int gb, int cb, bool bf16, int grid, int smem, cudaStream_t s);
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime (the library does not link against the driver).
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            p = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// rank-2 or rank-3 map with unit element strides, no interleave, no swizzle, zero fill outside the tensor
+bool encode(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
+            const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const cuuint32_t ones[3] = {1, 1, 1};
+    return fn(m, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
 
 int launch_pipe(const Args& a, int bits, bool bf16, const MmaPlan& pl, int debug, cudaStream_t s) {
     MmaArgs p{};
@@ -911,8 +1056,47 @@ int launch_pipe(const Args& a, int bits, bool bf16, const MmaPlan& pl, int debug
     p.debug = debug;
     p.wait_for_x = (a.rank > 0 && !pl.t_inline) ? 0 : 1;
     p.tile_aligned = 1;
-    return bits == 2 ? launch_pipe_int2(p, pl.gb, pl.chunk, bf16, pl.grid, pl.smem_bytes, s)
-                     : launch_pipe_int4(p, pl.gb, pl.chunk, bf16, pl.grid, pl.smem_bytes, s);
+
+    // Tensor maps.  Codes: the packed matrix seen as [group bytes][row][group] (strides 1, ldp, GB), box
+    // GB x 16 rows x CG groups -> one request per ring slot.  Should the driver refuse that view, the
+    // plain [row bytes][row] matrix with one GB x 16 box per group of a chunk serves instead.
+    PipeMaps tm{};
+    const int gb = pl.gb, cg = pl.chunk / gb;
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)gb, (cuuint64_t)a.n, (cuuint64_t)pl.ng};
+        const cuuint64_t strides[2] = {(cuuint64_t)a.ldp, (cuuint64_t)gb};
+        const cuuint32_t box[3] = {(cuuint32_t)gb, (cuuint32_t)kTileRows, (cuuint32_t)cg};
+        p.tma3d = (!(debug & QGEMV_DEBUG_BOX_PER_GROUP) && encode(&tm.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.packed, dims, strides, box)) ? 1 : 0;
+        if (!p.tma3d) {
+            const cuuint64_t dims2[2] = {(cuuint64_t)pl.ng * gb, (cuuint64_t)a.n};
+            const cuuint64_t strides2[1] = {(cuuint64_t)a.ldp};
+            const cuuint32_t box2[2] = {(cuuint32_t)gb, (cuuint32_t)kTileRows};
+            if (!encode(&tm.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.packed, dims2, strides2, box2)) {
+                set_error("qgemv_run: cuTensorMapEncodeTiled failed for the packed matrix");
+                return QGEMV_ERR_LAUNCH;
+            }
+        }
+    }
+    if (p.scales_async) {
+        const cuuint64_t dims[2] = {(cuuint64_t)pl.ng, (cuuint64_t)a.n};
+        const cuuint64_t strides[1] = {(cuuint64_t)a.lds * 2};
+        const cuuint32_t box[2] = {8, (cuuint32_t)kTileRows};
+        if (!encode(&tm.s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.scales, dims, strides, box)) p.scales_async = 0;
+    }
+    if (p.epi_async && a.oc > 0) {
+        const cuuint64_t dims[2] = {(cuuint64_t)a.oc, (cuuint64_t)a.n};
+        const cuuint64_t strides[1] = {(cuuint64_t)a.ldow * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)a.oc, (cuuint32_t)kTileRows};
+        if (!encode(&tm.ow, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.ow, dims, strides, box)) p.epi_async = 0;
+    }
+    if (p.epi_async && a.rank > 0) {
+        const cuuint64_t dims[2] = {(cuuint64_t)a.rank, (cuuint64_t)a.n};
+        const cuuint64_t strides[1] = {(cuuint64_t)a.ldu * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)a.rank, (cuuint32_t)kTileRows};
+        if (!encode(&tm.ru, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.ru, dims, strides, box)) p.epi_async = 0;
+    }
+    return bits == 2 ? launch_pipe_int2(p, tm, pl.gb, pl.chunk, bf16, pl.grid, pl.smem_bytes, s)
+                     : launch_pipe_int4(p, tm, pl.gb, pl.chunk, bf16, pl.grid, pl.smem_bytes, s);
 }
 #endif
 

@@ -8,6 +8,7 @@ uses host wall-clock); like the reference it re-runs the same buffers, so for ma
 than L2 these are warm-cache latencies -- ``bench.py`` measures the cold, HBM-bound case.
 
     python -m ai_accel_studio_b200.kernel_suite --m 1 --n 4096 --k 4096 --group-size 64
+    python -m ai_accel_studio_b200.kernel_suite --dequant          # the M > 4 path's dequantisation kernel
 """
 from __future__ import annotations
 
@@ -78,13 +79,45 @@ def run_kernel_suite(m=1, n=4096, k=4096, group_size=128, repeats=100, methods=N
     return rows
 
 
+def run_dequant_suite(shapes=((11008, 4096), (4096, 14336), (28672, 8192)), group_size=128, repeats=20):
+    """Microseconds and GB/s (packed bytes read + dense bytes written) of the dequantisation kernel that
+    feeds the M > 4 path, per bit width and output type.  Four output buffers are written in turn, so
+    the destination is never L2-resident."""
+    from . import ops
+    if not torch.cuda.is_available():
+        raise RuntimeError("the dequantisation suite requires an NVIDIA CUDA GPU")
+    rows = []
+    for n, k in shapes:
+        for bits in (2, 4):
+            packed = torch.randint(0, 256, (4, n, k * bits // 8), dtype=torch.uint8, device="cuda")
+            scales = (torch.rand((4, n, k // group_size), device="cuda") * 0.01 + 0.002).half()
+            for name in ("float16", "float32"):
+                def once(i):
+                    return ops.dequant(packed[i % 4], scales[i % 4], bits, group_size, k, name)
+                for i in range(4):
+                    once(i)
+                torch.cuda.synchronize()
+                st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                st.record()
+                for i in range(repeats):
+                    once(i)
+                en.record()
+                en.synchronize()
+                us = float(st.elapsed_time(en)) * 1e3 / repeats
+                moved = n * k * bits // 8 + n * (k // group_size) * 2 + n * k * (2 if name == "float16" else 4)
+                rows.append(dict(kernel="dequant", bits=bits, n=n, k=k, out=name, us=us, bytes=moved, GBps=moved / us / 1e3))
+    return rows
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
+    ap.add_argument("--dequant", action="store_true", help="time the dequantisation kernel instead of the decode rows")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--group-size", type=int, default=128)
     ap.add_argument("--repeats", type=int, default=500)
     a = ap.parse_args()
-    for row in run_kernel_suite(a.m, a.n, a.k, a.group_size, a.repeats):
+    rows = run_dequant_suite(group_size=a.group_size) if a.dequant else run_kernel_suite(a.m, a.n, a.k, a.group_size, a.repeats)
+    for row in rows:
         print(json.dumps(row))

@@ -110,6 +110,7 @@ class AllReduceLinear(nn.Module):
     replaying the same step without them."""
 
     skip_collective = False
+    one_shot = None          # a comm.OneShotAllReduce: used for the tensors it fits, NCCL for the rest
 
     def __init__(self, inner: nn.Module, group=None):
         super().__init__()
@@ -122,5 +123,9 @@ class AllReduceLinear(nn.Module):
             return y
         if torch.distributed.is_available() and torch.distributed.is_initialized() and \
                 torch.distributed.get_world_size(self.group) > 1:
-            torch.distributed.all_reduce(y, group=self.group)
+            comm = AllReduceLinear.one_shot
+            if comm is not None and comm.fits(y):
+                comm(y)
+            else:
+                torch.distributed.all_reduce(y, group=self.group)
         return y

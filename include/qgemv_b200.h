@@ -54,6 +54,7 @@ enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_M
 #define QGEMV_DEBUG_NO_L2_HINT 2
 #define QGEMV_DEBUG_CHUNK128 4   /* ring slots of 128 packed bytes per row instead of 256 */
 #define QGEMV_DEBUG_EARLY_TRIGGER 8   /* release the next launch at kernel entry instead of after the prologue */
+#define QGEMV_DEBUG_BOX_PER_GROUP 16  /* fill a ring slot with one copy request per group instead of one per slot */
 #define QGEMV_DEBUG_WARPS(n) (((n) & 0xff) << 8)
 #define QGEMV_DEBUG_STAGES(n) (((n) & 0xf) << 16)
 
