@@ -13,10 +13,10 @@ LIB_PATH = Path(__file__).resolve().parent / "libqgemv_b200.so"
 OK = 0
 ACT = {"none": 0, "relu": 1, "silu": 2, "swish": 2}
 F16, BF16, F32 = 0, 1, 2
-KERNEL = {"auto": 0, "simt": 1, "mma": 2, "mma_phased": 3}
+KERNEL = {"auto": 0, "simt": 1, "mma": 2, "mma_pipe": 3}
 DEBUG_DROP_PROJECTIONS, DEBUG_NO_L2_HINT = 1, 2
 MAX_M = 4
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_plan_describe", "qgemv_workspace_status", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem",
@@ -41,6 +41,7 @@ class Problem(C.Structure):
         ("res_v", C.c_void_p), ("ldv", C.c_int64),
         ("y", C.c_void_p), ("ldy", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_size_t),
     ]
 
 

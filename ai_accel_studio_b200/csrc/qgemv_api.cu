@@ -46,7 +46,7 @@ int validate(const qgemv_problem* p, size_t need) {
     if (!p->x || !p->packed || !p->scales || !p->y) { set_error("qgemv_run: x, packed, scales and y must be non-null"); return QGEMV_ERR_BAD_ARG; }
     if (p->act < QGEMV_ACT_NONE || p->act > QGEMV_ACT_SILU) { set_error("qgemv_run: unknown activation %d", p->act); return QGEMV_ERR_BAD_ARG; }
     if (p->x_dtype != QGEMV_F16 && p->x_dtype != QGEMV_BF16) { set_error("qgemv_run: activations must be fp16 or bf16"); return QGEMV_ERR_BAD_ARG; }
-    if (p->kernel < QGEMV_KERNEL_AUTO || p->kernel > QGEMV_KERNEL_MMA_PHASED) { set_error("qgemv_run: unknown kernel selector %d", p->kernel); return QGEMV_ERR_BAD_ARG; }
+    if (p->kernel < QGEMV_KERNEL_AUTO || p->kernel > QGEMV_KERNEL_MMA_PIPE) { set_error("qgemv_run: unknown kernel selector %d", p->kernel); return QGEMV_ERR_BAD_ARG; }
     if (p->outliers < 0 || (p->outliers > 0 && (!p->outlier_idx || !p->outlier_w))) { set_error("qgemv_run: outliers=%d needs outlier_idx and outlier_w", p->outliers); return QGEMV_ERR_BAD_ARG; }
     if (p->rank < 0 || (p->rank > 0 && (!p->res_u || !p->res_v))) { set_error("qgemv_run: rank=%d needs res_u and res_v", p->rank); return QGEMV_ERR_BAD_ARG; }
     if (p->rank > kMaxRank) { set_error("qgemv_run: residual rank %d exceeds the limit of %d", p->rank, kMaxRank); return QGEMV_ERR_TOO_LARGE; }
@@ -80,6 +80,12 @@ Args make_args(const qgemv_problem& p, size_t partial_floats) {
     a.m = p.m; a.n = p.n; a.kpad = p.k_padded; a.korig = p.k_original; a.group = p.group;
     a.act = p.act; a.oc = p.outliers; a.rank = p.rank;
     a.splits = 1; a.kspan = p.k_padded;
+    if (p.prefetch && p.prefetch_bytes >= 16 && reinterpret_cast<uintptr_t>(p.prefetch) % 16 == 0) {
+        a.hint = static_cast<const unsigned char*>(p.prefetch);
+        // at most 48 MB: two launches' worth of hints must sit in the 126 MB L2 beside what is being streamed
+        const size_t cap = (size_t)48 << 20;
+        a.hint_bytes = (long long)((p.prefetch_bytes < cap ? p.prefetch_bytes : cap) & ~(size_t)15);
+    }
     return a;
 }
 
@@ -103,21 +109,22 @@ extern "C" size_t qgemv_workspace_bytes(int bits, int m, int n, int k_padded, in
 
 namespace {
 
-// The kernel a valid problem gets: the pipelined tensor-core kernel, the phased one, or (ok == false)
-// the CUDA-core kernel.  `forced_missing` is set when the caller forced the MMA family and the shape
-// does not allow it.
+// The kernel a valid problem gets: the phased tensor-core kernel, its barrier-free variant when the
+// caller asks for it, or (ok == false) the CUDA-core kernel.  `forced_missing` is set when the caller
+// forced a tensor-core kernel and the shape does not allow it.
 MmaPlan choose(const qgemv_problem& p, size_t partial_floats, bool* forced_missing) {
     MmaPlan plan{};
     *forced_missing = false;
     if (p.kernel == QGEMV_KERNEL_SIMT) return plan;
     plan = plan_mma(p, partial_floats);
     if (!plan.ok) {
-        *forced_missing = p.kernel == QGEMV_KERNEL_MMA || p.kernel == QGEMV_KERNEL_MMA_PHASED;
+        *forced_missing = p.kernel == QGEMV_KERNEL_MMA || p.kernel == QGEMV_KERNEL_MMA_PIPE;
         return plan;
     }
-    if (p.kernel != QGEMV_KERNEL_MMA_PHASED) {
+    if (p.kernel == QGEMV_KERNEL_MMA_PIPE) {
         const MmaPlan pipe = plan_pipe(p, plan);
-        if (pipe.ok) return pipe;
+        if (!pipe.ok) *forced_missing = true;
+        return pipe;
     }
     return plan;
 }

@@ -44,6 +44,7 @@ struct Args {
     float* partial;           // split-K partials (workspace)
     float* tparts;            // per-K-part residual projections, 8-byte {value, tag} words (tail of the partial area)
     int m, n, kpad, korig, group, act, oc, rank;
+    const unsigned char* hint; long long hint_bytes;   // optional byte range to announce to L2 (the next GEMV's weights)
     int splits;               // number of K splits (grid.y)
     int kspan;                // codes per K split (multiple of the group)
 };
@@ -89,7 +90,7 @@ struct MmaPlan {
     int smem_bytes;         // dynamic shared memory
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
     int variant;            // 1: barrier-phased kernel (qgemv_mma.cu), 2: pipelined kernel (qgemv_pipe.cu)
-    int epi_tiles, t_pv, l2_chunks, off_cnt, off_red, off_bar;   // pipelined kernel only (see MmaArgs)
+    int epi_tiles, t_pv, l2_chunks, off_cnt, off_red;   // barrier-free kernel only (see MmaArgs)
     int chunk;              // pipelined kernel: packed bytes per row per ring slot (128 or 256)
     const char* name;
 };

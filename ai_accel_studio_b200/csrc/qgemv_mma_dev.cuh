@@ -30,15 +30,13 @@ struct MmaArgs {
     int off_tt;        // shared-memory table of t
     // dynamic shared memory layout (byte offsets)
     int off_xo, off_gx, off_slots, off_epi, off_meta, off_xs, off_ring;
-    // used by the pipelined kernel only
+    // used by the barrier-free kernel only
     int epi_tiles;     // tiles per CTA (its first ones) whose epilogue operands are prefetched into shared memory
     int t_pv;          // 16-byte pieces of res_v per thread of a residual-projection job
     int l2_chunks;     // chunks per warp announced to L2, beyond the ring, before the kernel waits for its predecessor
     int debug;         // qgemv_problem.debug
     int off_cnt;       // per-tile arrival counters of the CTA, followed by the "table of t is ready" flag
     int off_red;       // per-warp partial sums of a residual-projection job
-    int off_bar;       // mbarriers: one per ring slot per warp, then one for the epilogue operands
-    int tma3d;         // 1: one 3-D box per ring slot; 0: one 2-D box per group of the chunk
 };
 
 namespace {
@@ -267,9 +265,11 @@ __device__ __forceinline__ void epi_fold(float (&e0)[M], float (&e1)[M], int t, 
 // a launch starts with a cold instruction cache, and problems without these terms should not
 // have to step over their code.
 template <int M>
-__device__ __forceinline__ float4 tile_extras(const MmaArgs& p, const unsigned char* smem, int tile, const unsigned char* pre) {
+__device__ __forceinline__ float4 tile_extras(const MmaArgs& p, const unsigned char* smem, int tile, const unsigned char* pre,
+                                              int row_in_tile = -1) {
     const Args& a = p.a;
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    const int g = row_in_tile >= 0 ? row_in_tile : lane >> 2;      // tile row of this lane's first output row (second: + 8)
     const int c0 = min(tile * kTileRows + g, a.n - 1), c1 = min(tile * kTileRows + g + 8, a.n - 1);
     float e0[M], e1[M];
 #pragma unroll
@@ -291,14 +291,15 @@ __device__ __forceinline__ float4 tile_extras(const MmaArgs& p, const unsigned c
 
 template <int M, bool BF16, bool EX>
 __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned char* smem, int tile, float (&y)[4],
-                                            const unsigned char* pre) {
+                                            const unsigned char* pre, int row_in_tile = -1) {
     using XT = typename Act16<BF16>::T;
     const Args& a = p.a;
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    const int g = row_in_tile >= 0 ? row_in_tile : lane >> 2;      // tile row of this lane's first output row (second: + 8)
     const int r0 = tile * kTileRows + g, r1 = r0 + 8;
     const int c0 = min(r0, a.n - 1), c1 = min(r1, a.n - 1);
     if constexpr (EX) {
-        const float4 e = tile_extras<M>(p, smem, tile, pre);
+        const float4 e = tile_extras<M>(p, smem, tile, pre, row_in_tile);
         y[0] += e.x; y[1] += e.y; y[2] += e.z; y[3] += e.w;
         QTRACE(15);
     }

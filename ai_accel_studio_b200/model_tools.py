@@ -221,6 +221,35 @@ def build_mixed_model_streaming(shape: str, device, world: int = 1, layers: int 
     return model, plan
 
 
+def chain_weight_prefetch(model) -> int:
+    """Give every packed module of a decoder the weights of the Linear that runs after it as its L2
+    prefetch hint (``HybridPackedLinear.prefetch_next``): while one GEMV streams, the next one's packed
+    codes (or fp16 weight) are announced to L2.  Execution order: q, k, v, o, gate, up, down of each
+    layer, then the next layer, finally lm_head.  Call after the model is on its device (the hints
+    alias the modules' own tensors).  Returns the number of hints set."""
+    order = []
+    for layer in model.model.layers:
+        attn, mlp = layer.self_attn, layer.mlp
+        for holder, name in ((attn, "q_proj"), (attn, "k_proj"), (attn, "v_proj"), (attn, "o_proj"),
+                             (mlp, "gate_proj"), (mlp, "up_proj"), (mlp, "down_proj")):
+            mod = getattr(holder, name, None)
+            if mod is not None:
+                order.append(mod.inner if isinstance(mod, AllReduceLinear) else mod)
+    if getattr(model, "lm_head", None) is not None:
+        order.append(model.lm_head)
+
+    def main_tensor(mod):
+        if isinstance(mod, (HybridInt2Linear, HybridInt4Linear)):
+            return mod.packed
+        return getattr(mod, "weight", None)
+    n = 0
+    for cur, nxt in zip(order, order[1:]):
+        if isinstance(cur, (HybridInt2Linear, HybridInt4Linear)):
+            cur.prefetch_next = main_tensor(nxt)
+            n += cur.prefetch_next is not None
+    return n
+
+
 def fp16_weight_bytes(shape: str, world: int = 1) -> int:
     """Bytes of the fp16 model's weights on one rank (Linear layers split ``world`` ways, embeddings
     replicated, lm_head split by vocabulary rows)."""
@@ -277,7 +306,7 @@ def _timed_decode(dec, ids, new_tokens):
 
 def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
                      mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False,
-                     fuse_siblings=False, split=False, shard_vocab=True):
+                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=True):
     """Build (this rank's slice of) the model, optionally with the seeded mixed-bit plan, and run the
     fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts.
 
@@ -301,6 +330,8 @@ def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64,
     if mixed and fuse_siblings:
         from .optimize.siblings import fuse_decoder_siblings
         fused_groups = fuse_decoder_siblings(model)
+    if mixed and prefetch_hints and not fuse_siblings:
+        chain_weight_prefetch(model)
     g = torch.Generator().manual_seed(seed + 7)
     ids = torch.randint(0, SHAPES[shape]["vocab"], (batch, prompt_len), generator=g)
     res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=new_tokens, device=device,

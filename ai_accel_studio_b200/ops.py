@@ -89,7 +89,7 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
 
 
 def _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws,
-             bits, group, k_original, act, kernel) -> _cabi.Problem:
+             bits, group, k_original, act, kernel, prefetch=None) -> _cabi.Problem:
     m, kpad = x.shape
     p = _cabi.Problem()
     p.bits, p.m, p.n, p.k_padded, p.k_original, p.group = bits, m, packed.shape[0], kpad, k_original, group
@@ -109,6 +109,8 @@ def _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v,
         p.res_u, p.ldu, p.res_v, p.ldv = res_u.data_ptr(), res_u.stride(0), res_v.data_ptr(), res_v.stride(0)
     p.y, p.ldy = y.data_ptr(), y.stride(0)
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    if prefetch is not None and prefetch.is_cuda and prefetch.device == x.device:
+        p.prefetch, p.prefetch_bytes = prefetch.data_ptr(), prefetch.numel() * prefetch.element_size()
     return p
 
 
@@ -139,8 +141,12 @@ def _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res
 def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
          outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
          res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
-         bits: int, group: int, k_original: int, act: int, kernel: int) -> torch.Tensor:
+         bits: int, group: int, k_original: int, act: int, kernel: int,
+         prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4.
+
+    ``prefetch``: an optional (contiguous, static) tensor -- normally the packed codes of the GEMV that
+    follows -- which the kernel announces to L2 while it runs.
 
     Issued on the current stream with that stream's own scratch buffer (see ``ensure_workspace``), so
     GEMVs on different streams may overlap.  ``kernel``: ``_cabi.KERNEL[...]``, optionally OR-ed with
@@ -153,21 +159,22 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Opti
     ws = ensure_workspace(x.device)
     y = torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device=x.device)
     prob = _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws,
-                    bits, group, k_original, act, kernel)
+                    bits, group, k_original, act, kernel, prefetch)
     with torch.cuda.device(x.device):
         _cabi.run(prob, torch.cuda.current_stream().cuda_stream)
     return y
 
 
 @gemv.register_fake
-def _(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits, group, k_original, act, kernel):
+def _(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits, group, k_original, act, kernel, prefetch=None):
     return x.new_empty((x.shape[0], packed.shape[0]))
 
 
 def gemv_into(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
               outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
               res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
-              bits: int, group: int, k_original: int, act: int, kernel: int, out: torch.Tensor) -> torch.Tensor:
+              bits: int, group: int, k_original: int, act: int, kernel: int, out: torch.Tensor,
+              prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Same computation as ``gemv`` written into ``out`` ([M, N], x.dtype, unit inner stride).
 
     ``out`` is a CUDA tensor on x's device or a *pinned* host tensor: pinned memory is addressable by
@@ -189,7 +196,7 @@ def gemv_into(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias:
         res_u = res_v = None
     ws = ensure_workspace(x.device)
     prob = _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, out, ws,
-                    bits, group, k_original, act, kernel)
+                    bits, group, k_original, act, kernel, prefetch)
     with torch.cuda.device(x.device):
         _cabi.run(prob, torch.cuda.current_stream().cuda_stream)
     return out

@@ -52,6 +52,9 @@ class HybridPackedLinear(nn.Module):
     # of the right shape, so that replaying a decode step with and without the packed GEMVs tells how
     # much of the step they are.  Never set in production.
     skip_gemv: bool = False
+    # Optional hint for the decode path: a static tensor (normally the packed codes of the module that
+    # runs next) announced to L2 while this module's GEMV runs; see model_tools.chain_weight_prefetch.
+    prefetch_next = None
 
     def _finish_init(self, pw, k: int, n: int, source_bias):
         self.register_buffer("packed", pw.packed)
@@ -135,7 +138,7 @@ class HybridPackedLinear(nn.Module):
         return ops.gemv(xp, self.packed, self.scales, self.bias, self.outlier_idx if self.outlier_idx.numel() else None,
                         self.outlier_weight if self.outlier_idx.numel() else None,
                         self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
-                        self.bits, self.group_size, self.original_k, 0, self._kernel_code())
+                        self.bits, self.group_size, self.original_k, 0, self._kernel_code(), self.prefetch_next)
 
     def _kernel_code(self) -> int:
         from .. import _cabi
@@ -157,7 +160,7 @@ class HybridPackedLinear(nn.Module):
         return ops.gemv_into(xp, self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
                              self.outlier_weight if has_o else None,
                              self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
-                             self.bits, self.group_size, self.original_k, 0, self._kernel_code(), out)
+                             self.bits, self.group_size, self.original_k, 0, self._kernel_code(), out, self.prefetch_next)
 
     def _dense(self, xflat: torch.Tensor) -> torch.Tensor:
         from .. import ops

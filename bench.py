@@ -252,7 +252,7 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def time_resident_ring(w, ring, passes, steps, warmup, kernel, dev, rank, world, barrier):
+def time_resident_ring(w, ring, passes, steps, warmup, kernel, dev, rank, world, barrier, hints=True):
     """Device-resident leg for one workload: `ring` weight sets, one CUDA graph per pass, `passes`
     replays per step.  Returns (ms of the timed region, launches per GEMV, plan description, outputs, tensors)."""
     import torch
@@ -267,8 +267,10 @@ def time_resident_ring(w, ring, passes, steps, warmup, kernel, dev, rank, world,
 
     def gemv(i, x):
         s = sets[i]
+        # the hint a chain of layers gives: while set i streams, set i+1's packed codes are announced to L2
         return ops.gemv(x, s["packed"], s["scales"], None, s.get("outlier_idx"), s.get("outlier_weight"),
-                        s.get("res_u"), s.get("res_v"), bits, w["group"], k, 0, kernel)
+                        s.get("res_u"), s.get("res_v"), bits, w["group"], k, 0, kernel,
+                        sets[(i + 1) % ring]["packed"] if hints else None)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -384,7 +386,8 @@ def run_gpu_arm(args, w):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms, info, outs, t = time_resident_ring(w, RING, passes, args.steps, args.warmup, kernel, dev, rank, world, barrier)
+    ms, info, outs, t = time_resident_ring(w, RING, passes, args.steps, args.warmup, kernel, dev, rank, world, barrier,
+                                           hints=not args.no_prefetch_hints)
     sets, xs_host = t["sets"], t["xs_host"]
 
     # ---- end-to-end leg: host activations in, host results out, every GEMV ----------------------
@@ -409,9 +412,13 @@ def run_gpu_arm(args, w):
             self.group_size, self.out_features, self.graph_safe, self.kernel = w["group"], n, True, args.kernel
             self.debug = args.debug
             self.bias = None
+            self.prefetch_next = None
             self.residual_rank = w["rank"]
             self.res_u, self.res_v = s.get("res_u"), s.get("res_v")
     layers = [_Layer(s) for s in sets]
+    if not args.no_prefetch_hints:
+        for i, layer in enumerate(layers):
+            layer.prefetch_next = sets[(i + 1) % RING]["packed"]
     ys_host = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _ in range(RING)]
     xd_bufs = [torch.empty_like(x, device=dev) for x in xs_host]
     yd_bufs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(RING)]
@@ -481,7 +488,8 @@ def run_gpu_arm(args, w):
         w1 = WORKLOADS["c1"]
         ring1 = 64                                   # 64 x 4.7 MB = 303 MB > 2x L2
         passes1 = max(1, passes // 4)
-        ms1, info1, _, t1 = time_resident_ring(w1, ring1, passes1, args.steps, args.warmup, kernel, dev, rank, world, barrier)
+        ms1, info1, _, t1 = time_resident_ring(w1, ring1, passes1, args.steps, args.warmup, kernel, dev, rank, world, barrier,
+                                               hints=not args.no_prefetch_hints)
         del t1
         torch.cuda.empty_cache()
         if world > 1:
@@ -552,9 +560,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--passes", type=int, default=PASSES, help="passes over the ring of weight sets per step")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma", "mma_phased"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma", "mma_pipe"])
     ap.add_argument("--debug", type=lambda v: int(v, 0), default=0,
                     help="qgemv_problem.debug bits (tuning aids of the pipelined kernel; see include/qgemv_b200.h)")
+    ap.add_argument("--no-prefetch-hints", action="store_true",
+                    help="do not pass the next weight set's packed codes as the L2 prefetch hint of each GEMV")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-c1", action="store_true", help="skip the INT2 configuration leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode legs")

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define QGEMV_ABI_VERSION 2
+#define QGEMV_ABI_VERSION 3
 
 enum qgemv_status {
     QGEMV_OK = 0,
@@ -34,12 +34,15 @@ enum qgemv_status {
 enum qgemv_act { QGEMV_ACT_NONE = 0, QGEMV_ACT_RELU = 1, QGEMV_ACT_SILU = 2 };
 enum qgemv_dtype { QGEMV_F16 = 0, QGEMV_BF16 = 1, QGEMV_F32 = 2 };
 
-/* Which kernel family a call may use.  AUTO picks a tensor-core-assisted streaming kernel when
- * the shape allows it and the CUDA-core kernel otherwise; SIMT and MMA force a family.  Within
- * the MMA family the pipelined kernel (half an SM per CTA, weights prefetched before the wait for
- * the previous kernel) serves every shape whose CTAs can own whole 16-row tiles and the
- * barrier-phased kernel the rest; MMA_PHASED forces the latter (tests, A/B measurements). */
-enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_MMA = 2, QGEMV_KERNEL_MMA_PHASED = 3 };
+/* Which kernel a call may use.  AUTO picks the tensor-core-assisted streaming kernel (persistent
+ * grid, runs of a tile dealt over all CTAs, one CTA barrier between the streaming phase and the
+ * tile phase) when the shape allows it and the CUDA-core kernel otherwise; SIMT and MMA force one
+ * of the two.  MMA_PIPE asks for the barrier-free variant of the tensor-core kernel (whole 16-row
+ * tiles per CTA, per-tile arrival counters instead of the CTA barrier); it is measured slower than
+ * MMA on every benchmark shape (13.7 against 10.4 us on the headline one) and is kept for A/B
+ * measurements and as the base of further work, never chosen by AUTO.  A forced kernel that the
+ * shape does not allow returns QGEMV_ERR_SHAPE. */
+enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_MMA = 2, QGEMV_KERNEL_MMA_PIPE = 3 };
 
 #define QGEMV_MAX_M 4
 
@@ -50,11 +53,12 @@ enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_M
  * the workspace stays usable. */
 #define QGEMV_DEBUG_DROP_PROJECTIONS 1
 /* Tuning aids of the pipelined kernel (benchmarks only): do not announce the weights that follow
- * the ring to L2; smaller ring slots; force the warps per CTA (1..8) or the ring depth per warp (2..8). */
+ * the ring to L2; smaller or larger ring slots; force the warps per CTA (1..32) or the ring depth per warp (2..4). */
 #define QGEMV_DEBUG_NO_L2_HINT 2
 #define QGEMV_DEBUG_CHUNK128 4   /* ring slots of 128 packed bytes per row instead of 256 */
-#define QGEMV_DEBUG_EARLY_TRIGGER 8   /* release the next launch at kernel entry instead of after the prologue */
-#define QGEMV_DEBUG_BOX_PER_GROUP 16  /* fill a ring slot with one copy request per group instead of one per slot */
+#define QGEMV_DEBUG_LATE_TRIGGER 8    /* release the next launch after the x-dependent prologue instead of at kernel entry */
+#define QGEMV_DEBUG_CHUNK256 32       /* ring slots of 256 packed bytes per row even where smaller ones would employ more warps */
+#define QGEMV_DEBUG_SPLIT_FILL 64     /* before the dependency wait fill only the first ring slot; the rest follows the loads of x */
 #define QGEMV_DEBUG_WARPS(n) (((n) & 0xff) << 8)
 #define QGEMV_DEBUG_STAGES(n) (((n) & 0xf) << 16)
 
@@ -108,6 +112,11 @@ typedef struct qgemv_problem {
     const void* res_v;       int64_t ldv;
     void* y;                 int64_t ldy;
     void* workspace;         size_t workspace_bytes;
+    /* Optional hint: a byte range (16-byte aligned device memory, read-only while the call runs) that
+     * the kernel announces to L2 while it works -- typically the packed codes of the GEMV that follows
+     * in the stream, which then streams from L2 instead of DRAM.  Weights are static, so the hint can
+     * never be wrong, only useless.  NULL / 0: none.  Kernels that cannot use it ignore it. */
+    const void* prefetch;    size_t prefetch_bytes;
 } qgemv_problem;
 
 /* Fused small-M GEMV on `stream` (a cudaStream_t).  Capturable in a CUDA graph.

@@ -14,7 +14,7 @@ from ai_accel_studio_b200.kernels.decode_int2 import decode_int2_linear
 
 pytestmark = pytest.mark.gpu
 
-KERNELS = ("simt", "auto", "mma_phased")     # CUDA-core kernel, planner's choice, barrier-phased tensor-core kernel
+KERNELS = ("simt", "auto", "mma_pipe")     # CUDA-core kernel, planner's choice, barrier-free tensor-core kernel
 
 
 def _dev(pw):
@@ -23,8 +23,9 @@ def _dev(pw):
 
 def _run(bits, x, pw, **kw):
     fn = decode_int2_linear if bits == 2 else decode_int4_linear
-    if kw.get("kernel") == "mma_phased":
-        # shapes outside the tensor-core family (odd groups, unaligned rows) have no phased variant
+    if kw.get("kernel") == "mma_pipe":
+        # shapes outside the tensor-core family (odd groups, unaligned rows) or whose balance needs shared
+        # tiles have no barrier-free variant
         try:
             return fn(x, pw, **kw)
         except _cabi.QgemvError as e:

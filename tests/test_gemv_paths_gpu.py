@@ -3,7 +3,7 @@ qgemv_plan_describe, so that a later change of the planner cannot silently stop 
 
 * the barrier-phased kernel's tiles shared between CTAs (partial sums and arrival counters in the
   workspace, last arriver adds in CTA order),
-* the pipelined kernel's two ring geometries, forced warp / slot counts and its L2 announcements,
+* the pipelined kernel's ring geometries (128 / 256-byte slots), forced warp / slot counts and its L2 announcements,
 * chains of dependent launches (each kernel starts before its predecessor has finished and must
   wait for it before it reads x),
 * GEMVs that overlap on two streams with a workspace each,
@@ -119,8 +119,10 @@ PIPE_CASES = [
     (2, 4, 640, 14336, 256, 40, 16),
     (2, 1, 128, 896, 128, 8, 8),         # one chunk per tile: a single warp per CTA has work
 ]
-PIPE_VARIANTS = [0, _cabi.DEBUG_NO_L2_HINT, 4, 4 | _cabi.DEBUG_NO_L2_HINT, (3 << 8) | (2 << 16), 4 | (5 << 8) | (3 << 16),
-                 (8 << 8) | (2 << 16)]
+# debug bits: 2 no L2 announcements, 4 / 32 force 128 / 256-byte ring slots, 8 late release of the next launch;
+# bits 8.. force the warps per CTA, bits 16.. the ring depth
+PIPE_VARIANTS = [0, 2, 4, 4 | 2, 32, 8, (3 << 8) | (2 << 16), 4 | (5 << 8) | (3 << 16), (8 << 8) | (2 << 16),
+                 32 | (12 << 8) | (2 << 16), 4 | (16 << 8) | (2 << 16)]
 
 
 @pytest.mark.parametrize("bits,m,n,k,group,oc,rank", PIPE_CASES)
@@ -135,10 +137,12 @@ def test_pipelined_kernel_variants(bits, m, n, k, group, oc, rank, coracle):
     seen = {}
     for dbg in PIPE_VARIANTS:
         y = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
-        p = _problem(bits, m, n, k, group, oc, rank, d, y, ws, debug=dbg)
-        info = _cabi.plan_describe(p)
-        if dbg >> 8 and info.variant != 2:
-            continue                        # a forced warp count this shape has no work for: not a pipelined plan
+        p = _problem(bits, m, n, k, group, oc, rank, d, y, ws, kernel="mma_pipe", debug=dbg)
+        try:
+            info = _cabi.plan_describe(p)
+        except _cabi.QgemvError as e:
+            assert e.code == -2 and (dbg >> 8 or dbg & (4 | 32)), (dbg, e)
+            continue                        # a forced warp count or slot size this shape cannot use
         assert info.variant == 2 and info.tile_aligned == 1, (dbg, info.variant)
         for _ in range(2):
             assert lib.qgemv_run(ctypes.byref(p), ctypes.c_void_p(stream)) == 0, _cabi.last_error()
@@ -154,7 +158,7 @@ def test_pipelined_kernel_variants(bits, m, n, k, group, oc, rank, coracle):
     assert out.value == 0
 
 
-@pytest.mark.parametrize("kernel", ["auto", "mma_phased", "simt"])
+@pytest.mark.parametrize("kernel", ["auto", "mma_pipe", "simt"])
 def test_chain_of_dependent_launches(kernel):
     """x_{i+1} = y_i through 12 square GEMVs issued back to back: every launch is allowed to start
     (and to fetch its weights) while the previous one runs, and must still see the previous result.

@@ -160,7 +160,7 @@ def test_library_builds_loads_and_exports_header_symbols():
     l = _cabi.lib()
     assert l.qgemv_abi_version() == _cabi.ABI_VERSION
     assert _cabi.workspace_bytes(2, 1, 4096, 4096, 64, 0) >= 17408
-    assert ctypes.sizeof(_cabi.Problem) == l.qgemv_sizeof_problem() == 12 * 4 + 18 * 8
+    assert ctypes.sizeof(_cabi.Problem) == l.qgemv_sizeof_problem() == 12 * 4 + 20 * 8
 
 
 def test_c_abi_rejects_bad_problems_without_launching():
