@@ -39,6 +39,8 @@ def main():
                     help="also replay the decode step without the all-reduces / without the packed GEMVs and report their share")
     ap.add_argument("--replicated-lm-head", action="store_true",
                     help="tensor parallel: keep the whole output projection on every rank instead of vocab / world rows")
+    ap.add_argument("--nccl-all-reduce", action="store_true",
+                    help="tensor parallel: all-reduce the K-split projections with NCCL instead of the one-shot peer-memory kernel")
     a = ap.parse_args()
 
     import torch.distributed as dist
@@ -55,7 +57,7 @@ def main():
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
                                   a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers,
                                   fuse_siblings=a.fuse_siblings, split=a.split, shard_vocab=not a.replicated_lm_head,
-                                  prefetch_hints=not a.no_prefetch_hints)
+                                  prefetch_hints=not a.no_prefetch_hints, one_shot=not a.nccl_all_reduce)
         if world > 1:
             t = torch.tensor([res["aggregate_decode_tokens_s"]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)          # the slowest rank sets the pace
@@ -70,7 +72,8 @@ def main():
                         peak_vram_gb=res.get("peak_vram_gb"), cuda_graph=not a.no_graph,
                         compiled_layers=a.compile_layers, fused_sibling_groups=res.get("fused_sibling_groups", 0),
                         all_reduces_per_token=res.get("all_reduces_per_token"), packed_gemvs_per_token=res.get("packed_gemvs_per_token"),
-                        lm_head_rows_per_rank=res.get("lm_head_rows_per_rank"), split_ms_per_token=res.get("split_ms_per_token"))
+                        lm_head_rows_per_rank=res.get("lm_head_rows_per_rank"), all_reduce_impl=res.get("all_reduce_impl"),
+                        one_shot_status=res.get("one_shot_status"), split_ms_per_token=res.get("split_ms_per_token"))
             print(json.dumps(line), flush=True)
         del res
         gc.collect()

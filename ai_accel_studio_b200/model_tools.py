@@ -306,13 +306,15 @@ def _timed_decode(dec, ids, new_tokens):
 
 def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
                      mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False,
-                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=True):
+                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=True, one_shot=True):
     """Build (this rank's slice of) the model, optionally with the seeded mixed-bit plan, and run the
     fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts.
 
     ``split=True`` also replays the captured decode step without the all-reduces and without the
     packed GEMVs and reports the per-token milliseconds each of them accounts for
-    (``split_ms_per_token``: ``packed_gemv``, ``all_reduce``, ``other``)."""
+    (``split_ms_per_token``: ``packed_gemv``, ``all_reduce``, ``other``).  ``one_shot`` (world > 1, CUDA)
+    routes the K-split projections' all-reduces through the peer-memory kernel of ``comm.OneShotAllReduce``
+    instead of NCCL; ``all_reduce_impl`` in the result says which ran."""
     from .runtime_v5 import generate_static_benchmark, StaticGraphDecoder
     from .optimize._hybrid_base import HybridPackedLinear
     max_pos = prompt_len + new_tokens + 16
@@ -334,6 +336,29 @@ def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64,
         chain_weight_prefetch(model)
     g = torch.Generator().manual_seed(seed + 7)
     ids = torch.randint(0, SHAPES[shape]["vocab"], (batch, prompt_len), generator=g)
+    comm = None
+    if world > 1 and one_shot and torch.device(device).type == "cuda":
+        from .comm import OneShotAllReduce
+        # decode steps reduce [batch, hidden]; prefill reduces [batch * prompt_len, hidden] and stays with NCCL
+        comm = OneShotAllReduce(max_elems=-(-batch * SHAPES[shape]["hidden"] // 8) * 8, device=device)
+        AllReduceLinear.one_shot = comm
+    try:
+        res = _decode_benchmark_body(model, ids, shape, device, batch, prompt_len, new_tokens, mixed, world,
+                                     use_cuda_graph, compile_layers, vocab_shard, fused_groups, split)
+        res["all_reduce_impl"] = "none" if world <= 1 else ("one_shot_peer_memory" if comm is not None else "nccl")
+        if comm is not None:
+            res["one_shot_status"] = comm.status()
+    finally:
+        if comm is not None:
+            AllReduceLinear.one_shot = None
+            comm.close()
+    return res
+
+
+def _decode_benchmark_body(model, ids, shape, device, batch, prompt_len, new_tokens, mixed, world, use_cuda_graph,
+                           compile_layers, vocab_shard, fused_groups, split):
+    from .runtime_v5 import generate_static_benchmark, StaticGraphDecoder
+    from .optimize._hybrid_base import HybridPackedLinear
     res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=new_tokens, device=device,
                                     use_cuda_graph=use_cuda_graph, compile_layers=compile_layers, vocab_shard=vocab_shard)
     dec = res.pop("decoder")

@@ -112,6 +112,24 @@ class HybridPackedLinear(nn.Module):
             ops.ensure_workspace(packed.device)
         return self
 
+    def effective_weight(self) -> torch.Tensor:
+        """The float32 matrix this module multiplies by: dequantised base + outlier columns + U.V.
+        Plain torch ops on whatever device the buffers live on -- for construction-time error
+        analysis and the planner's quality measure, never for the forward pass."""
+        p = self.packed
+        if self.bits == 2:
+            codes = torch.stack([(p >> s) & 3 for s in (0, 2, 4, 6)], dim=-1).reshape(p.shape[0], -1).long()
+            from ..kernels.groupwise_int2 import INT2_LEVELS
+            vals = torch.tensor(INT2_LEVELS, device=p.device, dtype=torch.float32)[codes]
+        else:
+            vals = (torch.stack([p & 15, p >> 4], dim=-1).reshape(p.shape[0], -1).to(torch.int16) - 8).float()
+        w = (vals * self.scales.float().repeat_interleave(self.group_size, dim=1))[:, :self.original_k]
+        if self.outlier_idx.numel():
+            w[:, self.outlier_idx.long()] += self.outlier_weight.float()
+        if getattr(self, "residual_rank", 0):
+            w = w + self.res_u.float() @ self.res_v.float()
+        return w
+
     def set_residual(self, res_u: torch.Tensor, res_v: torch.Tensor) -> None:
         """Attach given low-rank factors ``res_u [N,r]``, ``res_v [r,K]`` (replacing any present)."""
         if res_u.shape[0] != self.out_features or res_v.shape[1] != self.in_features or res_u.shape[1] != res_v.shape[0]:

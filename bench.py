@@ -308,7 +308,7 @@ def decode_legs(args, dev, rank, world):
         legs = [("llama-3-8b", 1, 512, 128, (0.6, 0.3, 0.1)), ("llama-3-8b", 4, 512, 128, (0.6, 0.3, 0.1)),
                 ("llama-3-70b", 1, 1024, 128, (0.7, 0.3, 0.0))]
     else:
-        legs = [("llama-3-70b", 1, 1024, 128, (0.7, 0.3, 0.0))]
+        legs = [("llama-3-8b", 1, 512, 128, (0.6, 0.3, 0.1)), ("llama-3-70b", 1, 1024, 128, (0.7, 0.3, 0.0))]
     records, t_start = [], time.perf_counter()
     for shape, batch, prompt, new, probs in legs:
         rec = dict(shape=shape, batch=batch, prompt_tokens=prompt, new_tokens=new, tensor_parallel=world,
@@ -346,6 +346,7 @@ def decode_legs(args, dev, rank, world):
                                 packed_gemvs_per_token=res["packed_gemvs_per_token"],
                                 lm_head_rows_per_rank=res["lm_head_rows_per_rank"],
                                 split_ms_per_token=res.get("split_ms_per_token"),
+                                all_reduce_impl=res.get("all_reduce_impl"), one_shot_status=res.get("one_shot_status"),
                                 build_and_run_s=time.perf_counter() - t0)
             del res
             gc.collect()

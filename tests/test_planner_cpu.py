@@ -1,0 +1,71 @@
+"""The per-layer planner (candidate search, tie-breaking, fallbacks) against the decisions the
+reference planner took on the same seeded layers (tests/golden/planner_decisions.json, written by
+tests/golden/make_planner_golden.py).  CPU only: the timed gate reports "not measured" there, in
+the reference as here."""
+import json
+import math
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+sys.path.insert(0, str(GOLDEN))
+import planner_cases as pc                                              # noqa: E402
+
+from ai_accel_studio_b200.optimize import planner_v5 as pl             # noqa: E402
+
+WANT = json.loads((GOLDEN / "planner_decisions.json").read_text())
+V4_KEYS = ("group_sizes", "outliers", "residual_ranks", "nmse_limit", "cosine_limit")
+
+
+def _same(got: dict, want: dict):
+    for key in ("name", "method", "group_size", "outlier_columns", "residual_rank", "reason"):
+        assert got[key] == want[key], (key, got, want)
+    if "bits" in want:
+        assert got["bits"] == want["bits"]
+        for key in ("decode_speedup", "prefill_speedup", "projected_speedup"):
+            assert got[key] == want[key]
+    assert got["compression"] == pytest.approx(want["compression"], rel=1e-12)
+    if math.isinf(want["nmse"]):
+        assert math.isinf(got["nmse"])
+    else:   # the reference measures through a float32 CPU forward, this package through the reconstructed weight
+        assert got["nmse"] == pytest.approx(want["nmse"], rel=2e-3, abs=1e-9)
+        assert got["cosine"] == pytest.approx(want["cosine"], abs=1e-5)
+
+
+@pytest.mark.parametrize("name", pc.CASES)
+def test_decisions_match_the_reference_planner(name):
+    layer, x, kw = pc.make_case(name)
+    v4 = pl.decide_linear_v4(name, layer, x, **{k: v for k, v in kw.items() if k in V4_KEYS})
+    _same(v4.to_dict(), WANT[name]["v4"])
+    v5 = pl.decide_linear_v5(name, layer, x, **kw)
+    _same(v5.to_dict(), WANT[name]["v5"])
+
+
+def test_gate_rejects_slow_candidates(monkeypatch):
+    """An INT2 candidate that passes quality but is timed slower than fp16 gives way to INT4, and a
+    layer whose every candidate is slow stays fp16 (timings injected on the host)."""
+    layer, x, kw = pc.make_case("on_levels")
+    calls = []
+
+    def fake(layer_, cand, x_, tokens=64):
+        calls.append(cand.bits)
+        return (0.8, 1.0, 0.9) if cand.bits == 2 else (1.3, 0.9, 1.25)
+    monkeypatch.setattr(pl, "runtime_speedups", fake)
+    d = pl.decide_linear_v5("l", layer, x, **kw)
+    assert d.bits == 4 and d.reason.startswith("INT2 was slower than FP16") and d.decode_speedup == 1.3
+    assert calls[0] == 2 and set(calls[1:]) == {4}
+    monkeypatch.setattr(pl, "runtime_speedups", lambda *a, **k: (0.9, 0.9, 0.9))
+    d = pl.decide_linear_v5("l", layer, x, **kw)
+    assert d.method == "fp16" and d.bits == 16 and d.reason.startswith("kept FP16")
+
+
+def test_build_plan_and_capture():
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(128, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
+    caps = {"0": torch.randn(16, 128), "2": torch.randn(16, 64), "1": torch.randn(16, 64)}
+    plan = pl.build_plan_v5(model, caps)
+    assert [d.name for d in plan] == ["0", "2"]                         # the ReLU is not a Linear
+    assert all(isinstance(d, pl.LayerDecisionV5) for d in plan)
