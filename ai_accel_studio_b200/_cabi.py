@@ -16,7 +16,7 @@ F16, BF16, F32 = 0, 1, 2
 KERNEL = {"auto": 0, "simt": 1, "mma": 2, "mma_pipe": 3}
 DEBUG_DROP_PROJECTIONS, DEBUG_NO_L2_HINT = 1, 2
 MAX_M = 4
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_plan_describe", "qgemv_workspace_status", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem",

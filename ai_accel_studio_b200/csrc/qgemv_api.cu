@@ -44,7 +44,7 @@ int validate(const qgemv_problem* p, size_t need) {
     if (p->m < 1 || p->m > QGEMV_MAX_M) { set_error("qgemv_run: M must be 1..%d (got %d); larger batches use the dequantise + GEMM path", QGEMV_MAX_M, p->m); return QGEMV_ERR_BAD_ARG; }
     if (p->n < 1 || p->k_padded < 1 || p->k_original < 1 || p->k_original > p->k_padded) { set_error("qgemv_run: bad N / K (n=%d, k_padded=%d, k_original=%d)", p->n, p->k_padded, p->k_original); return QGEMV_ERR_BAD_ARG; }
     if (!p->x || !p->packed || !p->scales || !p->y) { set_error("qgemv_run: x, packed, scales and y must be non-null"); return QGEMV_ERR_BAD_ARG; }
-    if (p->act < QGEMV_ACT_NONE || p->act > QGEMV_ACT_SILU) { set_error("qgemv_run: unknown activation %d", p->act); return QGEMV_ERR_BAD_ARG; }
+    if (p->act < QGEMV_ACT_NONE || p->act > QGEMV_ACT_SILU_MUL) { set_error("qgemv_run: unknown activation %d", p->act); return QGEMV_ERR_BAD_ARG; }
     if (p->x_dtype != QGEMV_F16 && p->x_dtype != QGEMV_BF16) { set_error("qgemv_run: activations must be fp16 or bf16"); return QGEMV_ERR_BAD_ARG; }
     if (p->kernel < QGEMV_KERNEL_AUTO || p->kernel > QGEMV_KERNEL_MMA_PIPE) { set_error("qgemv_run: unknown kernel selector %d", p->kernel); return QGEMV_ERR_BAD_ARG; }
     if (p->outliers < 0 || (p->outliers > 0 && (!p->outlier_idx || !p->outlier_w))) { set_error("qgemv_run: outliers=%d needs outlier_idx and outlier_w", p->outliers); return QGEMV_ERR_BAD_ARG; }
@@ -52,7 +52,8 @@ int validate(const qgemv_problem* p, size_t need) {
     if (p->rank > kMaxRank) { set_error("qgemv_run: residual rank %d exceeds the limit of %d", p->rank, kMaxRank); return QGEMV_ERR_TOO_LARGE; }
     const int cpb = 8 / p->bits;
     if (p->group < cpb || p->group % cpb || p->k_padded % p->group) { set_error("qgemv_run: group=%d must be a multiple of %d and divide k_padded=%d", p->group, cpb, p->k_padded); return QGEMV_ERR_SHAPE; }
-    if (p->ldx < p->k_padded || p->ldy < p->n || p->ldp < (int64_t)p->k_padded / cpb || p->lds < p->k_padded / p->group) { set_error("qgemv_run: a leading dimension is smaller than its row"); return QGEMV_ERR_SHAPE; }
+    if (p->act == QGEMV_ACT_SILU_MUL && p->n % 16) { set_error("qgemv_run: the gated-pair activation needs N to be a multiple of 16 (got %d)", p->n); return QGEMV_ERR_SHAPE; }
+    if (p->ldx < p->k_padded || p->ldy < (p->act == QGEMV_ACT_SILU_MUL ? p->n / 2 : p->n) || p->ldp < (int64_t)p->k_padded / cpb || p->lds < p->k_padded / p->group) { set_error("qgemv_run: a leading dimension is smaller than its row"); return QGEMV_ERR_SHAPE; }
     if (p->outliers > 0 && p->ldow < p->outliers) { set_error("qgemv_run: ldow < outliers"); return QGEMV_ERR_SHAPE; }
     if (p->rank > 0 && (p->ldu < p->rank || p->ldv < p->k_original)) { set_error("qgemv_run: ldu < rank or ldv < k_original"); return QGEMV_ERR_SHAPE; }
     if (!aligned(p->x, 2) || !aligned(p->y, 2) || !aligned(p->scales, 2)) { set_error("qgemv_run: 16-bit tensors must be 2-byte aligned"); return QGEMV_ERR_ALIGN; }
@@ -115,10 +116,11 @@ namespace {
 MmaPlan choose(const qgemv_problem& p, size_t partial_floats, bool* forced_missing) {
     MmaPlan plan{};
     *forced_missing = false;
-    if (p.kernel == QGEMV_KERNEL_SIMT) return plan;
+    const bool needs_mma = p.act == QGEMV_ACT_SILU_MUL;      // the gated-pair epilogue exists in the tensor-core kernels only
+    if (p.kernel == QGEMV_KERNEL_SIMT) { *forced_missing = needs_mma; return plan; }
     plan = plan_mma(p, partial_floats);
     if (!plan.ok) {
-        *forced_missing = p.kernel == QGEMV_KERNEL_MMA || p.kernel == QGEMV_KERNEL_MMA_PIPE;
+        *forced_missing = needs_mma || p.kernel == QGEMV_KERNEL_MMA || p.kernel == QGEMV_KERNEL_MMA_PIPE;
         return plan;
     }
     if (p.kernel == QGEMV_KERNEL_MMA_PIPE) {
@@ -167,7 +169,7 @@ int run_checked(const qgemv_problem* p, void* stream, size_t need_bytes, size_t 
         if (r != QGEMV_OK) return r;
     }
     if (use_mma && plan.variant == 2) return launch_pipe(a, p->bits, bf16, plan, p->debug, s);
-    if (use_mma) return launch_mma(a, p->bits, bf16, plan, s);
+    if (use_mma) return launch_mma(a, p->bits, bf16, plan, p->debug, s);
     return launch_simt(a, p->bits, bf16, simt_unit_bytes(*p), s);
 }
 

@@ -95,7 +95,7 @@ struct MmaPlan {
     const char* name;
 };
 MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats);
-int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& plan, cudaStream_t s);
+int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& plan, int debug, cudaStream_t s);
 // The pipelined kernel takes the shapes whose CTAs own whole tiles; `base` is plan_mma's answer.
 MmaPlan plan_pipe(const qgemv_problem& p, const MmaPlan& base);
 int launch_pipe(const Args& a, int bits, bool bf16, const MmaPlan& plan, int debug, cudaStream_t s);

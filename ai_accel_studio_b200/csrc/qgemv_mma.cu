@@ -250,8 +250,10 @@ __device__ __noinline__ void build_t_table(const MmaArgs& p, unsigned char* smem
     const unsigned long long* src = reinterpret_cast<const unsigned long long*>(a.tparts);
     auto settle = [&](unsigned long long w, const unsigned long long* addr) {
         int spins = 0;
+        // about 30 ms; a few microseconds when a test makes the wait run out on purpose
+        const int limit = (p.debug & QGEMV_DEBUG_DROP_PROJECTIONS) ? (1 << 7) : (1 << 20);
         while ((unsigned)(w >> 32) != t_tag) {
-            if (++spins > (1 << 20)) { atomicExch(a.counters + kWsStatusIdx, 1); break; }
+            if (++spins > limit) { atomicExch(a.counters + kWsStatusIdx, 1); break; }
             __nanosleep(32);
             w = ld_relaxed_u64(addr);
         }
@@ -496,7 +498,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) qgemv_mma_kernel(const __gr
     for (int s = 1; s < GE::STAGES; ++s) issue_next(s);
     __syncthreads();                                  // staged activations visible to every warp
     QTRACE(2);
-    if (has_job && warp == 0) {
+    if (has_job && warp == 0 && !(p.debug & QGEMV_DEBUG_DROP_PROJECTIONS)) {
         // The warps' partial sums were written before the barrier above: add them in warp order and
         // publish {sum, launch tag} for every CTA's epilogue with one relaxed 64-bit store.
         const float* red = reinterpret_cast<const float*>(smem + p.off_tt);
@@ -840,7 +842,7 @@ MmaPlan plan_mma(const qgemv_problem& p, size_t partial_floats) {
     return pl;
 }
 
-int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, cudaStream_t s) {
+int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, int debug, cudaStream_t s) {
     MmaArgs p{};
     p.a = a;
     p.nt = pl.nt; p.nch = pl.nch; p.ng = pl.ng;
@@ -855,6 +857,7 @@ int launch_mma(const Args& a, int bits, bool bf16, const MmaPlan& pl, cudaStream
     p.off_meta = pl.off_meta; p.off_xs = pl.off_xs; p.off_ring = pl.off_ring;
     p.t_inline = pl.t_inline; p.t_parts = pl.t_parts; p.off_tt = pl.off_tt;
     p.wait_for_x = (a.rank > 0 && !pl.t_inline) ? 0 : 1;
+    p.debug = debug;
     p.tile_aligned = pl.tile_aligned;
     return bits == 2 ? launch_mma_int2(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s)
                      : launch_mma_int4(p, pl.gb, bf16, pl.grid, pl.smem_bytes, s);

@@ -313,6 +313,21 @@ __device__ __forceinline__ void finish_tile(const MmaArgs& p, const unsigned cha
             b0 = __half2float(a.bias[c0]); b1 = __half2float(a.bias[c1]);
         }
     }
+    if (a.act == QGEMV_ACT_SILU_MUL) {
+        // rows g and g + 8 of the tile are a (gate, up) pair, both held by this lane: one output per pair,
+        // rounded where separate 16-bit operators would round
+        auto r16 = [](float v) { return Act16<BF16>::to_float(Act16<BF16>::from_float(v)); };
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int m = 2 * t + h;
+            if (m < M) {
+                const float gate = r16(y[h] + b0), up = r16(y[2 + h] + b1);
+                const float s = r16(gate / (1.0f + __expf(-gate)));
+                out[(size_t)m * a.ldy + tile * (kTileRows / 2) + g] = Act16<BF16>::from_float(s * up);
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int m = 2 * t + h;

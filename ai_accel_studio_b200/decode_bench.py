@@ -33,8 +33,8 @@ def main():
                     help="fuse the non-GEMV work of each decoder layer with torch.compile (regional compilation)")
     ap.add_argument("--fuse-siblings", action="store_true",
                     help="merge q/k/v and gate/up projections that share bit width and group size into one launch each")
-    ap.add_argument("--no-prefetch-hints", action="store_true",
-                    help="do not announce the next Linear's weights to L2 while a packed GEMV runs")
+    ap.add_argument("--prefetch-hints", action="store_true",
+                    help="announce the next Linear's weights to L2 while a packed GEMV runs (honoured by the mma_pipe kernel only)")
     ap.add_argument("--split", action="store_true",
                     help="also replay the decode step without the all-reduces / without the packed GEMVs and report their share")
     ap.add_argument("--replicated-lm-head", action="store_true",
@@ -57,7 +57,7 @@ def main():
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
                                   a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers,
                                   fuse_siblings=a.fuse_siblings, split=a.split, shard_vocab=not a.replicated_lm_head,
-                                  prefetch_hints=not a.no_prefetch_hints, one_shot=not a.nccl_all_reduce)
+                                  prefetch_hints=a.prefetch_hints, one_shot=not a.nccl_all_reduce)
         if world > 1:
             t = torch.tensor([res["aggregate_decode_tokens_s"]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)          # the slowest rank sets the pace

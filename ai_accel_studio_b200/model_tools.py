@@ -245,8 +245,10 @@ def chain_weight_prefetch(model) -> int:
     n = 0
     for cur, nxt in zip(order, order[1:]):
         if isinstance(cur, (HybridInt2Linear, HybridInt4Linear)):
-            cur.prefetch_next = main_tensor(nxt)
-            n += cur.prefetch_next is not None
+            t = main_tensor(nxt)
+            if t is not None and not t.is_meta:
+                cur.__dict__["prefetch_next"] = t.detach()      # a plain attribute: never a parameter or buffer
+                n += 1
     return n
 
 
@@ -306,7 +308,7 @@ def _timed_decode(dec, ids, new_tokens):
 
 def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
                      mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False,
-                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=True, one_shot=True):
+                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=False, one_shot=True):
     """Build (this rank's slice of) the model, optionally with the seeded mixed-bit plan, and run the
     fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts.
 

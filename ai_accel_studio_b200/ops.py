@@ -88,6 +88,18 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
         raise RuntimeError(f"{name} must be a CUDA tensor: this build has no CPU path")
 
 
+ACT_SILU_MUL = 3      # qgemv_act: rows are (8 gate, 8 up) blocks, the output is silu(gate) * up of width N / 2
+
+
+def _out_width(packed: torch.Tensor, act: int) -> int:
+    n = int(packed.shape[0])
+    if act == ACT_SILU_MUL:
+        if n % 16:
+            raise ValueError("the gated-pair activation needs an even number of 8-row blocks (N % 16 == 0)")
+        return n // 2
+    return n
+
+
 def _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws,
              bits, group, k_original, act, kernel, prefetch=None) -> _cabi.Problem:
     m, kpad = x.shape
@@ -143,7 +155,8 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Opti
          res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
          bits: int, group: int, k_original: int, act: int, kernel: int,
          prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4.
+    """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4
+    (``act`` 0 none, 1 ReLU, 2 SiLU; 3 = gated pairs, see ``ACT_SILU_MUL``: y is then [M, N/2]).
 
     ``prefetch``: an optional (contiguous, static) tensor -- normally the packed codes of the GEMV that
     follows -- which the kernel announces to L2 while it runs.
@@ -157,7 +170,7 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Opti
     if res_u is not None and res_u.numel() == 0:
         res_u = res_v = None
     ws = ensure_workspace(x.device)
-    y = torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device=x.device)
+    y = torch.empty((x.shape[0], _out_width(packed, act)), dtype=x.dtype, device=x.device)
     prob = _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws,
                     bits, group, k_original, act, kernel, prefetch)
     with torch.cuda.device(x.device):
@@ -167,7 +180,7 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Opti
 
 @gemv.register_fake
 def _(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits, group, k_original, act, kernel, prefetch=None):
-    return x.new_empty((x.shape[0], packed.shape[0]))
+    return x.new_empty((x.shape[0], _out_width(packed, act)))
 
 
 def gemv_into(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
@@ -183,8 +196,8 @@ def gemv_into(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias:
     reads them).  A plain function, not a registered op: it mutates its argument and is meant for
     serving loops, eager or captured in a CUDA graph."""
     _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits)
-    if out.dtype != x.dtype or out.ndim != 2 or tuple(out.shape) != (x.shape[0], packed.shape[0]) or out.stride(1) != 1:
-        raise ValueError("out must be [M, N] of x.dtype with unit inner stride")
+    if out.dtype != x.dtype or out.ndim != 2 or tuple(out.shape) != (x.shape[0], _out_width(packed, act)) or out.stride(1) != 1:
+        raise ValueError("out must be [M, N] ([M, N/2] for the gated-pair activation) of x.dtype with unit inner stride")
     if out.is_cuda:
         if out.device != x.device:
             raise RuntimeError("out must be on x's device")

@@ -55,6 +55,9 @@ class HybridPackedLinear(nn.Module):
     # Optional hint for the decode path: a static tensor (normally the packed codes of the module that
     # runs next) announced to L2 while this module's GEMV runs; see model_tools.chain_weight_prefetch.
     prefetch_next = None
+    # Set by siblings.merge_gate_up: the rows are (8 gate, 8 up) blocks of a feed-forward block's two
+    # input projections and forward returns silu(gate(x)) * up(x), of width out_features = rows / 2.
+    gated_pairs: bool = False
 
     def _finish_init(self, pw, k: int, n: int, source_bias):
         self.register_buffer("packed", pw.packed)
@@ -125,14 +128,14 @@ class HybridPackedLinear(nn.Module):
             vals = (torch.stack([p & 15, p >> 4], dim=-1).reshape(p.shape[0], -1).to(torch.int16) - 8).float()
         w = (vals * self.scales.float().repeat_interleave(self.group_size, dim=1))[:, :self.original_k]
         if self.outlier_idx.numel():
-            w[:, self.outlier_idx.long()] += self.outlier_weight.float()
+            w.index_add_(1, self.outlier_idx.long(), self.outlier_weight.float())     # repeated columns add up
         if getattr(self, "residual_rank", 0):
             w = w + self.res_u.float() @ self.res_v.float()
         return w
 
     def set_residual(self, res_u: torch.Tensor, res_v: torch.Tensor) -> None:
         """Attach given low-rank factors ``res_u [N,r]``, ``res_v [r,K]`` (replacing any present)."""
-        if res_u.shape[0] != self.out_features or res_v.shape[1] != self.in_features or res_u.shape[1] != res_v.shape[0]:
+        if res_u.shape[0] != self.packed.shape[0] or res_v.shape[1] != self.in_features or res_u.shape[1] != res_v.shape[0]:
             raise ValueError("res_u must be [N,r] and res_v [r,K]")
         dev = self.packed.device
         for name in ("res_u", "res_v"):
@@ -156,7 +159,7 @@ class HybridPackedLinear(nn.Module):
         return ops.gemv(xp, self.packed, self.scales, self.bias, self.outlier_idx if self.outlier_idx.numel() else None,
                         self.outlier_weight if self.outlier_idx.numel() else None,
                         self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
-                        self.bits, self.group_size, self.original_k, 0, self._kernel_code(), self.prefetch_next)
+                        self.bits, self.group_size, self.original_k, 3 if self.gated_pairs else 0, self._kernel_code(), self.prefetch_next)
 
     def _kernel_code(self) -> int:
         from .. import _cabi
@@ -178,7 +181,7 @@ class HybridPackedLinear(nn.Module):
         return ops.gemv_into(xp, self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
                              self.outlier_weight if has_o else None,
                              self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
-                             self.bits, self.group_size, self.original_k, 0, self._kernel_code(), out, self.prefetch_next)
+                             self.bits, self.group_size, self.original_k, 3 if self.gated_pairs else 0, self._kernel_code(), out, self.prefetch_next)
 
     def _dense(self, xflat: torch.Tensor) -> torch.Tensor:
         from .. import ops
@@ -189,6 +192,9 @@ class HybridPackedLinear(nn.Module):
             y = y + F.linear(xflat[:, self.outlier_idx.long()], self.outlier_weight.to(xflat.dtype))
         if self.residual_rank:
             y = y + F.linear(F.linear(xflat.to(self.res_v.dtype), self.res_v), self.res_u).to(y.dtype)
+        if self.gated_pairs:
+            pairs = y.view(y.shape[0], -1, 2, 8)
+            y = (F.silu(pairs[:, :, 0, :]) * pairs[:, :, 1, :]).reshape(y.shape[0], -1)
         return y
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -11,6 +11,13 @@ into one module of the same class with no change to the kernel:
 * low-rank residual: block structure, ``U = diag(U_1, U_2, ...)`` and ``V = [V_1; V_2; ...]``, so row
   block i only sees its own ``U_i (V_i x)``.
 
+Gate / up pairs go one step further (``merge_gate_up``): their rows are interleaved in blocks of 8
+(8 gate rows, then the 8 up rows with the same indices), which puts every (gate_j, up_j) pair into
+one lane of the kernel's 16-row output tile, so the epilogue computes ``silu(gate) * up`` itself and
+stores ``[M, intermediate]`` directly (``QGEMV_ACT_SILU_MUL``): gate projection, up projection,
+activation and product become one launch.  Both intermediate results and the activation are rounded
+to the activation type exactly where separate operators would round them.
+
 ``merge_packed`` does that algebra (any device).  ``fuse_decoder_siblings`` rewires a Hugging Face
 Llama / Qwen2 style decoder in place: the first sibling called computes the fused result, the
 others take their slice of it.  Per row the quantised term is bit-identical to the unfused module
@@ -101,6 +108,51 @@ def merge_packed(mods):
     return fused, sizes
 
 
+def can_merge_gate_up(gate, up) -> bool:
+    """Mergeable siblings of equal width whose row count fills whole 8-row blocks, on the tensor-core
+    kernels' shapes (16-byte aligned packed rows and a supported group size)."""
+    if not can_merge([gate, up]) or gate.out_features != up.out_features or gate.out_features % 8:
+        return False
+    group_bytes = gate.group_size * gate.bits // 8
+    return group_bytes in (16, 32, 64) and gate.packed.shape[1] % 16 == 0 and gate.padded_k % 8 == 0
+
+
+@torch.no_grad()
+def merge_gate_up(gate, up):
+    """One packed module computing ``silu(gate(x)) * up(x)``: ``merge_packed`` followed by the 8-row
+    interleave of the two halves.  ``out_features`` of the result is the intermediate size."""
+    if not can_merge_gate_up(gate, up):
+        raise ValueError("gate / up projections cannot be merged into a gated pair")
+    fused, sizes = merge_packed([gate, up])
+    n = sizes[0]
+    rows = torch.arange(n, device=fused.packed.device).view(n // 8, 1, 8)
+    perm = torch.cat([rows, rows + n], dim=1).reshape(-1)            # block b: gate rows 8b..8b+7, up rows 8b..8b+7
+    for name in ("packed", "scales", "outlier_weight", "bias", "res_u"):
+        t = getattr(fused, name, None)
+        if t is not None and t.shape[0] == 2 * n:
+            fused._buffers[name] = t[perm].contiguous()
+    fused.gated_pairs = True
+    fused.out_features = n
+    return fused
+
+
+class GatedFeedForward(nn.Module):
+    """Stands where a Llama / Qwen2 style feed-forward block stood: ``down(silu(gate(x)) * up(x))`` with
+    the part in parentheses computed by one fused packed module."""
+
+    def __init__(self, gate_up: HybridPackedLinear, down_proj: nn.Module):
+        super().__init__()
+        self.gate_up = gate_up
+        self.down_proj = down_proj
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(self.gate_up(x))
+
+
+def _is_silu(fn) -> bool:
+    return isinstance(fn, nn.SiLU) or fn is torch.nn.functional.silu or type(fn).__name__ in ("SiLUActivation", "SiLU")
+
+
 class _SiblingSlice(nn.Module):
     """Stands where one sibling Linear stood.  All slices of a group share one fused module; the
     first slice called with a given activation tensor runs it, the others reuse that result."""
@@ -136,11 +188,22 @@ class _SiblingGroup:
         return parts
 
 
-def fuse_decoder_siblings(model: nn.Module, sets=SIBLING_SETS) -> int:
+def fuse_decoder_siblings(model: nn.Module, sets=SIBLING_SETS, gated=True) -> int:
     """Replace mergeable sibling sets (same parent module, see ``SIBLING_SETS``) by slices of one fused
     packed module each.  Returns the number of groups fused.  Siblings that differ in bit width or
-    group size, or are not packed modules, are left alone."""
+    group size, or are not packed modules, are left alone.  With ``gated`` a feed-forward block whose
+    gate / up projections merge and whose activation is SiLU becomes a ``GatedFeedForward`` (one launch
+    for both projections, the activation and the product)."""
     fused_groups = 0
+    if gated:
+        for name, parent in list(model.named_modules()):
+            for child_name, mlp in list(parent.named_children()):
+                g, u, d = (getattr(mlp, n, None) for n in ("gate_proj", "up_proj", "down_proj"))
+                if g is None or u is None or d is None or not _is_silu(getattr(mlp, "act_fn", None)):
+                    continue
+                if isinstance(g, HybridPackedLinear) and isinstance(u, HybridPackedLinear) and can_merge_gate_up(g, u):
+                    setattr(parent, child_name, GatedFeedForward(merge_gate_up(g, u), d))
+                    fused_groups += 1
     for parent in list(model.modules()):
         for names in sets:
             mods = [getattr(parent, n, None) for n in names]

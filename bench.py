@@ -388,7 +388,7 @@ def run_gpu_arm(args, w):
     if sampler:
         sampler.start()
     ms, info, outs, t = time_resident_ring(w, RING, passes, args.steps, args.warmup, kernel, dev, rank, world, barrier,
-                                           hints=not args.no_prefetch_hints)
+                                           hints=args.prefetch_hints)
     sets, xs_host = t["sets"], t["xs_host"]
 
     # ---- end-to-end leg: host activations in, host results out, every GEMV ----------------------
@@ -417,7 +417,7 @@ def run_gpu_arm(args, w):
             self.residual_rank = w["rank"]
             self.res_u, self.res_v = s.get("res_u"), s.get("res_v")
     layers = [_Layer(s) for s in sets]
-    if not args.no_prefetch_hints:
+    if args.prefetch_hints:
         for i, layer in enumerate(layers):
             layer.prefetch_next = sets[(i + 1) % RING]["packed"]
     ys_host = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _ in range(RING)]
@@ -490,7 +490,7 @@ def run_gpu_arm(args, w):
         ring1 = 64                                   # 64 x 4.7 MB = 303 MB > 2x L2
         passes1 = max(1, passes // 4)
         ms1, info1, _, t1 = time_resident_ring(w1, ring1, passes1, args.steps, args.warmup, kernel, dev, rank, world, barrier,
-                                               hints=not args.no_prefetch_hints)
+                                               hints=args.prefetch_hints)
         del t1
         torch.cuda.empty_cache()
         if world > 1:
@@ -564,8 +564,8 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma", "mma_pipe"])
     ap.add_argument("--debug", type=lambda v: int(v, 0), default=0,
                     help="qgemv_problem.debug bits (tuning aids of the pipelined kernel; see include/qgemv_b200.h)")
-    ap.add_argument("--no-prefetch-hints", action="store_true",
-                    help="do not pass the next weight set's packed codes as the L2 prefetch hint of each GEMV")
+    ap.add_argument("--prefetch-hints", action="store_true",
+                    help="pass the next weight set's packed codes as the L2 prefetch hint of each GEMV (honoured by --kernel mma_pipe only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-c1", action="store_true", help="skip the INT2 configuration leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode legs")

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define QGEMV_ABI_VERSION 3
+#define QGEMV_ABI_VERSION 4
 
 enum qgemv_status {
     QGEMV_OK = 0,
@@ -31,7 +31,16 @@ enum qgemv_status {
     QGEMV_ERR_TOO_LARGE = -6     /* a size exceeds a stated fixed limit */
 };
 
-enum qgemv_act { QGEMV_ACT_NONE = 0, QGEMV_ACT_RELU = 1, QGEMV_ACT_SILU = 2 };
+/* SILU_MUL fuses the gated product of a feed-forward block (act_fn(gate_proj(x)) * up_proj(x)) into the
+ * epilogue of ONE launch over both projections.  The N weight rows (N a multiple of 16) come in blocks
+ * of 16: 8 rows of the gate projection followed by the 8 matching rows of the up projection, and the
+ * output is [M, N/2]:
+ *     y[m, 8b + j] = r( r(silu(r(v[m, 16b + j]))) * r(v[m, 16b + 8 + j]) )
+ * with v the result before activation (bias included) and r() rounding to the activation type -- the
+ * roundings a 16-bit framework makes when it runs the two projections, the activation and the product
+ * as separate operators.  ldy >= N/2.  Tensor-core kernels only (QGEMV_ERR_SHAPE where the shape needs
+ * the CUDA-core kernel).  No counterpart in the reference, which launches the three operators apart. */
+enum qgemv_act { QGEMV_ACT_NONE = 0, QGEMV_ACT_RELU = 1, QGEMV_ACT_SILU = 2, QGEMV_ACT_SILU_MUL = 3 };
 enum qgemv_dtype { QGEMV_F16 = 0, QGEMV_BF16 = 1, QGEMV_F32 = 2 };
 
 /* Which kernel a call may use.  AUTO picks the tensor-core-assisted streaming kernel (persistent

@@ -243,7 +243,8 @@ def test_two_streams_overlap_with_a_workspace_each():
         assert ops.workspace_status("cuda", s[i]) == 0
 
 
-def test_projection_wait_runs_out_and_is_reported(coracle):
+@pytest.mark.parametrize("kernel", ["auto", "mma_pipe"])
+def test_projection_wait_runs_out_and_is_reported(kernel, coracle):
     """QGEMV_DEBUG_DROP_PROJECTIONS: the CTAs that compute the residual projections keep them to
     themselves and the readers' wait is cut to a few microseconds.  The launch must end by itself,
     raise the workspace's status word, and leave the workspace and the device usable."""
@@ -259,9 +260,9 @@ def test_projection_wait_runs_out_and_is_reported(coracle):
         torch.cuda.synchronize()
         return out.value
     y = torch.zeros((m, n), dtype=torch.float16, device="cuda")
-    p = _problem(bits, m, n, k, group, oc, rank, d, y, ws)
+    p = _problem(bits, m, n, k, group, oc, rank, d, y, ws, kernel=kernel)
     info = _cabi.plan_describe(p)
-    assert info.variant == 2 and info.inline_projections == 1
+    assert info.variant == (2 if kernel == "mma_pipe" else 1) and info.inline_projections == 1
     assert lib.qgemv_run(ctypes.byref(p), ctypes.c_void_p(stream)) == 0      # a normal launch first
     torch.cuda.synchronize()
     ref = _oracle(coracle, bits, k, group, h)

@@ -210,3 +210,55 @@ def test_kernel_suite_rows_and_speed_gate():
     cand = HybridInt4Linear(lin, 128, None, 8).cuda()
     d, p_, proj = runtime_speedups(lin, cand, torch.randn(32, 1024, device="cuda", dtype=torch.float16))
     assert d > 0 and p_ > 0 and proj > 0
+
+
+def _r16(t, dtype):
+    return t.to(dtype).float()
+
+
+@pytest.mark.parametrize("bits,dtype", [(4, torch.float16), (2, torch.float16), (4, torch.bfloat16)])
+def test_gated_pair_epilogue(bits, dtype):
+    """gate / up merged with their rows interleaved in blocks of 8: one launch returns
+    silu(gate(x)) * up(x), rounded where separate 16-bit operators round; compared with the oracle's
+    float32 projections pushed through those roundings, with the unfused modules, and on the M > 4 path."""
+    from ai_accel_studio_b200 import _cabi, ops
+    from ai_accel_studio_b200.optimize.siblings import merge_gate_up
+    torch.manual_seed(20 + bits)
+    k, n = 1024, 2048 + 64
+    cls = HybridInt2Linear if bits == 2 else HybridInt4Linear
+    gate = cls(nn.Linear(k, n, bias=True), 128, None, 16)
+    up = cls(nn.Linear(k, n, bias=False), 128, None, 8)
+    up.set_residual(torch.randn(n, 8) * 0.02, torch.randn(8, k) * 0.02)
+    fused = merge_gate_up(gate, up).cuda()
+    gate, up = gate.cuda(), up.cuda()
+
+    def np_(t):
+        return t.cpu().numpy()
+    for m_rows in (1, 3, 4):
+        x = (torch.randn(m_rows, k) * 1.5).to(dtype).cuda()
+        y = fused(x)
+        assert y.shape == (m_rows, n) and y.dtype == dtype
+        xs = x.float().cpu().numpy().astype(np.float32)
+        refs = []
+        for mod in (gate, up):
+            pw = O.PackedWeight(bits, np_(mod.packed), np_(mod.scales), k, k, 128)
+            refs.append(torch.from_numpy(O.gemv_f32(
+                xs if dtype == torch.bfloat16 else np_(x), pw, None if mod.bias is None else np_(mod.bias), np_(mod.outlier_idx),
+                np_(mod.outlier_weight), np_(mod.res_u) if mod.residual_rank else None,
+                np_(mod.res_v) if mod.residual_rank else None)).float())
+        g16, u16 = _r16(refs[0], dtype), _r16(refs[1], dtype)
+        want = _r16(_r16(torch.nn.functional.silu(g16), dtype) * u16, dtype)
+        tol = 1.6e-2 if dtype == torch.bfloat16 else 2e-3        # two units in the last place: a rounding may flip per stage
+        err = (y.float().cpu() - want).abs()
+        assert float((err / (tol * want.abs() + 1e-2)).max()) <= 1.0, float(err.max())
+        sep = torch.nn.functional.silu(gate(x)) * up(x)
+        assert float((y.float() - sep.float()).abs().max()) <= 2e-2 * float(sep.float().abs().max()) + 1e-3
+    x8 = torch.randn(9, k).to(dtype).cuda()                                        # M > 4: dequantise + GEMM, then the same pairing
+    y8, sep8 = fused(x8), torch.nn.functional.silu(gate(x8)) * up(x8)
+    assert y8.shape == (9, n)
+    assert float((y8.float() - sep8.float()).abs().max()) <= 2e-2 * float(sep8.float().abs().max()) + 1e-3
+    with pytest.raises(_cabi.QgemvError) as e:                                      # no gated epilogue in the CUDA-core kernel
+        ops.gemv(x8[:1].contiguous(), fused.packed, fused.scales, fused.bias, fused.outlier_idx, fused.outlier_weight, fused.res_u,
+                 fused.res_v, bits, 128, k, ops.ACT_SILU_MUL, _cabi.KERNEL["simt"])
+    assert e.value.code == -2
+    assert ops.workspace_status("cuda") == 0

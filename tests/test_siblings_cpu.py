@@ -98,3 +98,51 @@ def test_rewiring_calls_the_fused_module_once_per_activation():
     x2 = torch.randn(2, 128)
     layer.self_attn.q_proj(x2), layer.self_attn.k_proj(x2), layer.self_attn.v_proj(x2)
     assert len(calls) == 2
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_gate_up_interleave_describes_the_same_rows(bits):
+    """merge_gate_up: block b of the fused module holds gate rows 8b..8b+7 then up rows 8b..8b+7, with
+    every per-row tensor permuted alike (checked through the oracle on each half)."""
+    from ai_accel_studio_b200.optimize.siblings import can_merge_gate_up, merge_gate_up
+    torch.manual_seed(10 + bits)
+    k, n = 256, 48
+    cls = HybridInt2Linear if bits == 2 else HybridInt4Linear
+    gate = cls(nn.Linear(k, n, bias=True), 64, None, 8)
+    up = cls(nn.Linear(k, n, bias=False), 64, None, 4)
+    gate.set_residual(torch.randn(n, 4) * 0.05, torch.randn(4, k) * 0.05)
+    assert can_merge_gate_up(gate, up)
+    fused = merge_gate_up(gate, up)
+    assert fused.gated_pairs and fused.out_features == n and fused.packed.shape[0] == 2 * n and type(fused) is cls
+    x = (torch.randn(3, k) * 0.5).half().numpy()
+    both = _oracle(fused, x).reshape(3, n // 8, 2, 8)
+    np.testing.assert_allclose(both[:, :, 0, :].reshape(3, n), _oracle(gate, x), rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(both[:, :, 1, :].reshape(3, n), _oracle(up, x), rtol=1e-5, atol=1e-6)
+    assert not can_merge_gate_up(gate, cls(nn.Linear(k, n + 8), 64, None, 0))       # widths differ
+    assert not can_merge_gate_up(cls(nn.Linear(k, 12), 64, None, 0), cls(nn.Linear(k, 12), 64, None, 0))   # not whole blocks
+    with pytest.raises(ValueError):
+        merge_gate_up(gate, (HybridInt4Linear if bits == 2 else HybridInt2Linear)(nn.Linear(k, n), 64, None, 0))
+
+
+def test_decoder_rewiring_builds_gated_feed_forward():
+    from ai_accel_studio_b200.optimize.siblings import GatedFeedForward
+
+    class MLP(nn.Module):
+        def __init__(self, act):
+            super().__init__()
+            self.gate_proj = HybridInt4Linear(nn.Linear(128, 64, bias=False), 64, None, 0)
+            self.up_proj = HybridInt4Linear(nn.Linear(128, 64, bias=False), 64, None, 0)
+            self.down_proj = nn.Linear(64, 128, bias=False)
+            self.act_fn = act
+
+    class Layer(nn.Module):
+        def __init__(self, act):
+            super().__init__()
+            self.mlp = MLP(act)
+
+    torch.manual_seed(3)
+    model = nn.ModuleList([Layer(nn.SiLU()), Layer(nn.GELU())])
+    assert fuse_decoder_siblings(model) == 2                     # one gated block, one plain gate/up merge
+    assert isinstance(model[0].mlp, GatedFeedForward) and model[0].mlp.gate_up.gated_pairs
+    assert not isinstance(model[1].mlp, GatedFeedForward)        # another activation: only the launches are merged
+    assert fuse_decoder_siblings(nn.ModuleList([Layer(nn.SiLU())]), gated=False) == 1
