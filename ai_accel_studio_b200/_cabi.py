@@ -21,7 +21,8 @@ ABI_VERSION = 4
 EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_plan_describe", "qgemv_workspace_status", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem",
            "qcomm_slot_bytes", "qcomm_flag_bytes", "qcomm_state_bytes", "qcomm_allreduce", "qcomm_status", "qcomm_alloc", "qcomm_free",
-           "qcomm_ipc_export", "qcomm_ipc_open", "qcomm_ipc_close")
+           "qcomm_ipc_export", "qcomm_ipc_open", "qcomm_ipc_close",
+           "qdec_rmsnorm", "qdec_rope_append", "qdec_attention_workspace_bytes", "qdec_attention", "qdec_silu_mul")
 COMM_MAX_RANKS, COMM_MAX_BLOCKS, COMM_IPC_HANDLE_BYTES = 8, 64, 64
 
 
@@ -113,6 +114,17 @@ def lib():
     l.qcomm_ipc_open.restype = C.c_int
     l.qcomm_ipc_close.argtypes = [C.c_void_p]
     l.qcomm_ipc_close.restype = C.c_int
+    i64, vp, ci = C.c_int64, C.c_void_p, C.c_int
+    l.qdec_rmsnorm.argtypes = [vp, i64, vp, i64, vp, vp, i64, ci, ci, C.c_float, ci, vp]
+    l.qdec_rmsnorm.restype = ci
+    l.qdec_rope_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, ci, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]
+    l.qdec_rope_append.restype = ci
+    l.qdec_attention_workspace_bytes.argtypes = [ci] * 5
+    l.qdec_attention_workspace_bytes.restype = C.c_size_t
+    l.qdec_attention.argtypes = [vp, i64, vp, vp, vp, vp, i64, ci, ci, ci, ci, ci, C.c_float, vp, C.c_size_t, ci, vp]
+    l.qdec_attention.restype = ci
+    l.qdec_silu_mul.argtypes = [vp, i64, vp, i64, vp, i64, ci, ci, ci, vp]
+    l.qdec_silu_mul.restype = ci
     l.qdequant.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
                            C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     l.qdequant.restype = C.c_int

@@ -21,6 +21,7 @@ UNITS = [
     ("qgemv_simt.cu", [], "qgemv_simt.o"),
     ("qdequant.cu", [], "qdequant.o"),
     ("qcomm.cu", [], "qcomm.o"),
+    ("qdecode.cu", [], "qdecode.o"),
     ("qgemv_mma.cu", ["-DQGEMV_INST_BITS=2"], "qgemv_mma_int2.o"),
     ("qgemv_mma.cu", ["-DQGEMV_INST_BITS=4"], "qgemv_mma_int4.o"),
     ("qgemv_pipe.cu", ["-DQGEMV_INST_BITS=2"], "qgemv_pipe_int2.o"),

@@ -39,6 +39,9 @@ def main():
                     help="also replay the decode step without the all-reduces / without the packed GEMVs and report their share")
     ap.add_argument("--replicated-lm-head", action="store_true",
                     help="tensor parallel: keep the whole output projection on every rank instead of vocab / world rows")
+    ap.add_argument("--framework-step", action="store_true",
+                    help="run the work between the GEMVs (norms, rotary embedding, attention, SwiGLU) with the framework's "
+                         "operators instead of this package's decode-step kernels")
     ap.add_argument("--nccl-all-reduce", action="store_true",
                     help="tensor parallel: all-reduce the K-split projections with NCCL instead of the one-shot peer-memory kernel")
     a = ap.parse_args()
@@ -57,7 +60,7 @@ def main():
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
                                   a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers,
                                   fuse_siblings=a.fuse_siblings, split=a.split, shard_vocab=not a.replicated_lm_head,
-                                  prefetch_hints=a.prefetch_hints, one_shot=not a.nccl_all_reduce)
+                                  prefetch_hints=a.prefetch_hints, one_shot=not a.nccl_all_reduce, native_step=False if a.framework_step else None)
         if world > 1:
             t = torch.tensor([res["aggregate_decode_tokens_s"]], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)          # the slowest rank sets the pace
@@ -72,7 +75,7 @@ def main():
                         peak_vram_gb=res.get("peak_vram_gb"), cuda_graph=not a.no_graph,
                         compiled_layers=a.compile_layers, fused_sibling_groups=res.get("fused_sibling_groups", 0),
                         all_reduces_per_token=res.get("all_reduces_per_token"), packed_gemvs_per_token=res.get("packed_gemvs_per_token"),
-                        lm_head_rows_per_rank=res.get("lm_head_rows_per_rank"), all_reduce_impl=res.get("all_reduce_impl"),
+                        lm_head_rows_per_rank=res.get("lm_head_rows_per_rank"), all_reduce_impl=res.get("all_reduce_impl"), decode_step=res.get("decode_step"),
                         one_shot_status=res.get("one_shot_status"), split_ms_per_token=res.get("split_ms_per_token"))
             print(json.dumps(line), flush=True)
         del res

@@ -308,7 +308,7 @@ def _timed_decode(dec, ids, new_tokens):
 
 def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64, probs=(0.6, 0.3, 0.1),
                      mixed=True, world=1, layers=None, seed=0, use_cuda_graph=True, compile_layers=False,
-                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=False, one_shot=True):
+                     fuse_siblings=False, split=False, shard_vocab=True, prefetch_hints=False, one_shot=True, native_step=None):
     """Build (this rank's slice of) the model, optionally with the seeded mixed-bit plan, and run the
     fixed-length greedy decode benchmark.  Returns the runtime's result dict plus weight-byte counts.
 
@@ -346,7 +346,7 @@ def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64,
         AllReduceLinear.one_shot = comm
     try:
         res = _decode_benchmark_body(model, ids, shape, device, batch, prompt_len, new_tokens, mixed, world,
-                                     use_cuda_graph, compile_layers, vocab_shard, fused_groups, split)
+                                     use_cuda_graph, compile_layers, vocab_shard, fused_groups, split, native_step)
         res["all_reduce_impl"] = "none" if world <= 1 else ("one_shot_peer_memory" if comm is not None else "nccl")
         if comm is not None:
             res["one_shot_status"] = comm.status()
@@ -358,11 +358,12 @@ def decode_benchmark(shape: str, device, batch=1, prompt_len=128, new_tokens=64,
 
 
 def _decode_benchmark_body(model, ids, shape, device, batch, prompt_len, new_tokens, mixed, world, use_cuda_graph,
-                           compile_layers, vocab_shard, fused_groups, split):
+                           compile_layers, vocab_shard, fused_groups, split, native_step=None):
     from .runtime_v5 import generate_static_benchmark, StaticGraphDecoder
     from .optimize._hybrid_base import HybridPackedLinear
     res = generate_static_benchmark(model, input_ids=ids, max_new_tokens=new_tokens, device=device,
-                                    use_cuda_graph=use_cuda_graph, compile_layers=compile_layers, vocab_shard=vocab_shard)
+                                    use_cuda_graph=use_cuda_graph, compile_layers=compile_layers, vocab_shard=vocab_shard,
+                                    native_step=native_step)
     dec = res.pop("decoder")
     res.update(linear_weight_bytes(model))
     res["shape"], res["mixed"], res["world"] = shape, mixed, world
@@ -380,7 +381,8 @@ def _decode_benchmark_body(model, ids, shape, device, batch, prompt_len, new_tok
                 continue
             setattr(holder, attr, True)
             try:
-                d2 = StaticGraphDecoder(model, batch, prompt_len + new_tokens + 8, device=device, vocab_shard=vocab_shard)
+                d2 = StaticGraphDecoder(model, batch, prompt_len + new_tokens + 8, device=device, vocab_shard=vocab_shard,
+                                        native_step=False if compile_layers else native_step)
                 d2.prefill(ids_d)
                 d2.capture()
                 without, _ = _timed_decode(d2, ids_d, new_tokens)

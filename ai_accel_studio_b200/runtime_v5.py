@@ -81,9 +81,14 @@ class StaticGraphDecoder:
     """
 
     def __init__(self, model, batch_size: int, max_cache_len: int, device=None, dtype=None, compile_layers=False,
-                 vocab_shard=None, group=None):
+                 vocab_shard=None, group=None, native_step=None):
         from transformers import StaticCache
         self.model = model
+        # The decode step between the GEMVs: this package's kernels (decode_step.NativeDecodeStep) where the
+        # model's architecture allows, else the framework's forward.  None = decide by the model.
+        self.native = None
+        self.native_reason = None
+        self._want_native = native_step
         self.vocab_rank, self.vocab_world = vocab_shard if vocab_shard is not None else (0, 1)
         self.group = group
         if compile_layers:
@@ -113,10 +118,28 @@ class StaticGraphDecoder:
         best = every[..., 0].argmax(0)                                                               # first maximum: lowest rank, lowest index
         return every[best, torch.arange(mine.shape[0], device=mine.device), 1].long().unsqueeze(-1)
 
+    def _bind_native(self):
+        """After the first prefill (the cache allocates its tensors lazily): build the native decode step."""
+        if self.native is not None or self._want_native is False or self.native_reason is not None:
+            return
+        from . import decode_step
+        if self.device.type != "cuda":
+            self.native_reason = "not a CUDA device"
+        else:
+            self.native_reason = decode_step.unsupported_reason(self.model)
+        if self.native_reason is None:
+            self.native = decode_step.NativeDecodeStep(self.model, self.cache, self.batch, self.max_len)
+        elif self._want_native:
+            raise NotImplementedError(f"native decode step: {self.native_reason}")
+
     @torch.no_grad()
     def _step(self):
-        out = self.model(input_ids=self.tok, past_key_values=self.cache, cache_position=self.pos, use_cache=True)
-        nxt = self._greedy(out.logits[:, -1])
+        if self.native is not None:
+            logits = self.native.step(self.tok, self.pos)
+        else:
+            out = self.model(input_ids=self.tok, past_key_values=self.cache, cache_position=self.pos, use_cache=True)
+            logits = out.logits[:, -1]
+        nxt = self._greedy(logits)
         self.tok.copy_(nxt)
         self.pos.add_(1)
         return nxt
@@ -132,6 +155,7 @@ class StaticGraphDecoder:
         nxt = self._greedy(out.logits[:, -1])
         self.tok.copy_(nxt)
         self.pos.fill_(n)
+        self._bind_native()
         return nxt
 
     @torch.no_grad()
@@ -171,7 +195,8 @@ class StaticGraphDecoder:
 
 @torch.no_grad()
 def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens=64, device="cuda", warmups=2,
-                              input_ids=None, use_cuda_graph=True, compile_layers=False, vocab_shard=None, group=None):
+                              input_ids=None, use_cuda_graph=True, compile_layers=False, vocab_shard=None, group=None,
+                              native_step=None):
     """Fixed-length greedy generation benchmark (reference protocol, ai_accel_lab/runtime_v5.py:29-73).
 
     Either ``tokenizer`` + ``prompt`` (left-padded to a multiple of 8, as the reference does) or
@@ -196,7 +221,7 @@ def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens
     b, n = input_ids.shape
     cuda = torch.device(device).type == "cuda"
     dec = StaticGraphDecoder(model, b, n + int(max_new_tokens) + 8, device=device, compile_layers=compile_layers,
-                             vocab_shard=vocab_shard, group=group)
+                             vocab_shard=vocab_shard, group=group, native_step=False if compile_layers else native_step)
 
     for _ in range(max(1, int(warmups))):
         dec.prefill(input_ids)
@@ -232,7 +257,8 @@ def generate_static_benchmark(model, tokenizer=None, prompt=None, max_new_tokens
                decode_tokens_s=generated / (decode_ms / 1000.0), total_tokens_s=generated / (total_ms / 1000.0),
                aggregate_decode_tokens_s=b * generated / (decode_ms / 1000.0),
                aggregate_total_tokens_s=b * generated / (total_ms / 1000.0),
-               decode_ms_per_token=decode_ms / generated, batch=b, tokens=out, decoder=dec)
+               decode_ms_per_token=decode_ms / generated, batch=b, tokens=out, decoder=dec,
+               decode_step="native" if dec.native is not None else f"framework ({dec.native_reason or 'native step not requested'})")
     if cuda:
         res.update(peak_vram_gb=torch.cuda.max_memory_allocated() / 1024 ** 3,
                    current_vram_gb=torch.cuda.memory_allocated() / 1024 ** 3,

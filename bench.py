@@ -331,7 +331,7 @@ def decode_legs(args, dev, rank, world):
             t0 = time.perf_counter()
             try:
                 res = mt.decode_benchmark(shape, dev, batch, prompt, new, probs, variant == "mixed", world,
-                                          split=True, shard_vocab=True)
+                                          split=True, shard_vocab=True, fuse_siblings=True)
             except torch.cuda.OutOfMemoryError:
                 rec[variant] = dict(skipped="out of device memory")
                 gc.collect()
@@ -347,6 +347,7 @@ def decode_legs(args, dev, rank, world):
                                 lm_head_rows_per_rank=res["lm_head_rows_per_rank"],
                                 split_ms_per_token=res.get("split_ms_per_token"),
                                 all_reduce_impl=res.get("all_reduce_impl"), one_shot_status=res.get("one_shot_status"),
+                                decode_step=res.get("decode_step"), fused_sibling_groups=res.get("fused_sibling_groups"),
                                 build_and_run_s=time.perf_counter() - t0)
             del res
             gc.collect()

@@ -149,10 +149,11 @@ def test_library_builds_loads_and_exports_header_symbols():
     assert lib_path.exists()
     header = "\n".join(p.read_text() for p in sorted((ROOT / "include").glob("*.h")))
     declared = set(re.findall(r"^\s*(?:const\s+)?[A-Za-z_][\w\s\*]*?\b(q[a-z_0-9]+)\s*\(", header, flags=re.M))
-    declared = {d for d in declared if d.startswith(("qgemv_", "qdequant", "qunpack", "qcomm_"))}
+    declared = {d for d in declared if d.startswith(("qgemv_", "qdequant", "qunpack", "qcomm_", "qdec_"))}
     assert {"qgemv_run", "qgemv_run_static", "qgemv_workspace_bytes", "qgemv_plan_name", "qgemv_plan_describe",
             "qgemv_workspace_status", "qdequant", "qunpack_codes", "qgemv_error_string", "qgemv_abi_version",
-            "qcomm_allreduce", "qcomm_status", "qcomm_alloc", "qcomm_ipc_export", "qcomm_ipc_open"} <= declared
+            "qcomm_allreduce", "qcomm_status", "qcomm_alloc", "qcomm_ipc_export", "qcomm_ipc_open",
+            "qdec_rmsnorm", "qdec_rope_append", "qdec_attention", "qdec_attention_workspace_bytes", "qdec_silu_mul"} <= declared
     raw = ctypes.CDLL(str(lib_path))
     for name in declared:
         assert hasattr(raw, name), f"{name} is declared in the header but not exported"
