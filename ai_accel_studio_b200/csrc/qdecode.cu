@@ -4,6 +4,8 @@
 // one launch per step of the layer, coalesced 8 / 16-byte accesses, enough CTAs for the attention
 // to spread the cache over the SMs, and no waiting between CTAs (the attention's slices meet through
 // an arrival counter: whoever comes last merges).
+#include <type_traits>
+
 #include "qgemv_common.cuh"
 #include "../../include/qdecode_b200.h"
 
@@ -140,9 +142,9 @@ __global__ void __launch_bounds__(128) rope_append_kernel(void* q_, long long ld
 }
 
 // ---------------------------------------------------------------------------------------------
-// attention of one query token per sequence: grid (slice, kv head, sequence), 4 warps per CTA
+// attention of one query token per sequence: grid (slice, kv head, sequence), 8 warps per CTA
 // ---------------------------------------------------------------------------------------------
-constexpr int kAttWarps = 4;
+constexpr int kAttWarps = 8;
 constexpr int kAttMaxSlices = 16;
 constexpr int kAttMinSlice = 16;                 // positions: shorter slices are not worth a CTA
 
@@ -191,27 +193,32 @@ __global__ void __launch_bounds__(kAttWarps * 32) attention_kernel(const void* q
 #pragma unroll
         for (int e = 0; e < E; ++e) o[g][e] = 0.0f;
     }
-    auto load = [&](const T* p, float (&dst)[E]) {
-        if constexpr (E == 4) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(p);
-            const T* el = reinterpret_cast<const T*>(&raw);
+    // Raw 4 / 8-byte pieces of a cache row; converted only when their turn comes, so that the loads of the
+    // next pair of positions stay in flight while this pair is processed (a warp issues in order: the
+    // first instruction that needs a pending load stalls everything behind it).
+    using Raw = typename std::conditional<E == 4, uint2, uint32_t>::type;
+    auto widen = [&](const Raw& raw, float (&dst)[E]) {
+        const T* el = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) dst[e] = Act16<BF16>::to_float(el[e]);
-        } else {
-            const uint32_t raw = *reinterpret_cast<const uint32_t*>(p);
-            const T* el = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-            for (int e = 0; e < 2; ++e) dst[e] = Act16<BF16>::to_float(el[e]);
-        }
+        for (int e = 0; e < E; ++e) dst[e] = Act16<BF16>::to_float(el[e]);
     };
-    // two positions per iteration: their reductions are independent and overlap
-    for (int p0 = s0 + warp * 2; p0 < s1; p0 += kAttWarps * 2) {
+    constexpr int STEP = kAttWarps * 2;           // two positions per warp and iteration: independent reductions overlap
+    int p0 = s0 + warp * 2;
+    Raw rk0 = {}, rv0 = {}, rk1 = {}, rv1 = {};
+    auto fetch = [&](int p, Raw& a, Raw& b, Raw& c, Raw& d) {
+        const size_t pa = (size_t)min(p, s1 - 1) * D, pb = (size_t)min(p + 1, s1 - 1) * D;
+        a = *reinterpret_cast<const Raw*>(kbase + pa);
+        b = *reinterpret_cast<const Raw*>(vbase + pa);
+        c = *reinterpret_cast<const Raw*>(kbase + pb);
+        d = *reinterpret_cast<const Raw*>(vbase + pb);
+    };
+    if (p0 < s1) fetch(p0, rk0, rv0, rk1, rv1);
+    for (; p0 < s1; p0 += STEP) {
+        Raw nk0, nv0, nk1, nv1;
+        fetch(p0 + STEP, nk0, nv0, nk1, nv1);       // clamped to the slice: the last iteration re-reads its final row
         const bool two = p0 + 1 < s1;
         float k0[E], k1[E], v0[E], v1[E];
-        load(kbase + (size_t)p0 * D, k0);
-        load(vbase + (size_t)p0 * D, v0);
-        load(kbase + (size_t)(two ? p0 + 1 : p0) * D, k1);
-        load(vbase + (size_t)(two ? p0 + 1 : p0) * D, v1);
+        widen(rk0, k0); widen(rv0, v0); widen(rk1, k1); widen(rv1, v1);
         float sc0[G], sc1[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -230,14 +237,15 @@ __global__ void __launch_bounds__(kAttWarps * 32) attention_kernel(const void* q
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const float s1v = two ? sc1[g] : -1.0e30f;
-            const float mn = fmaxf(m[g], fmaxf(sc0[g], s1v));
-            const float alpha = __expf(m[g] - mn), p0w = __expf(sc0[g] - mn), p1w = two ? __expf(s1v - mn) : 0.0f;
+            const float second = two ? sc1[g] : -1.0e30f;
+            const float mn = fmaxf(m[g], fmaxf(sc0[g], second));
+            const float alpha = __expf(m[g] - mn), p0w = __expf(sc0[g] - mn), p1w = two ? __expf(second - mn) : 0.0f;
             m[g] = mn;
             l[g] = l[g] * alpha + p0w + p1w;
 #pragma unroll
             for (int e = 0; e < E; ++e) o[g][e] = fmaf(p1w, v1[e], fmaf(p0w, v0[e], o[g][e] * alpha));
         }
+        rk0 = nk0; rv0 = nv0; rk1 = nk1; rv1 = nv1;
     }
 
     // the CTA's warps meet in shared memory
@@ -251,7 +259,7 @@ __global__ void __launch_bounds__(kAttWarps * 32) attention_kernel(const void* q
         for (int e = 0; e < E; ++e) sm_o[warp][g][lane * E + e] = o[g][e];
     }
     __syncthreads();
-    constexpr int STRIDE = D + 2;                 // floats per (slice, head): m, l, o[D]
+    constexpr int STRIDE = D + 4;                 // floats per (slice, head): m, l, two unused, o[D] (16-byte aligned)
     float* mine = parts + ((((size_t)b * hkv + kvh) * slices + slice) * G) * STRIDE;
     for (int i = tid; i < G * D; i += kAttWarps * 32) {
         const int g = i / D, dd = i - g * D;
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(kAttWarps * 32) attention_kernel(const void* q
             acc = fmaf(sm_o[w][g][dd], f, acc);
             ll = fmaf(sm_l[w][g], f, ll);
         }
-        mine[g * STRIDE + 2 + dd] = acc;
+        mine[g * STRIDE + 4 + dd] = acc;
         if (dd == 0) { mine[g * STRIDE] = mm; mine[g * STRIDE + 1] = ll; }
     }
     // arrival: the last CTA of this (sequence, kv head) merges the slices; nobody waits
@@ -278,20 +286,44 @@ __global__ void __launch_bounds__(kAttWarps * 32) attention_kernel(const void* q
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Every load of the merge is independent of the others and issued before the first use: one
+    // trip to L2 per head instead of one per slice.  A warp takes a head; a lane takes 4 output elements.
     const float* all = parts + (((size_t)b * hkv + kvh) * slices) * G * STRIDE;
     T* out = static_cast<T*>(out_) + (size_t)b * ldo + (size_t)kvh * G * D;
-    for (int i = tid; i < G * D; i += kAttWarps * 32) {
-        const int g = i / D, dd = i - g * D;
-        float mm = -1.0e30f;
-        for (int s = 0; s < slices; ++s) mm = fmaxf(mm, __ldcg(all + ((size_t)s * G + g) * STRIDE));
-        float acc = 0.0f, ll = 0.0f;
-        for (int s = 0; s < slices; ++s) {
-            const float* pp = all + ((size_t)s * G + g) * STRIDE;
-            const float f = __expf(__ldcg(pp) - mm);
-            ll = fmaf(__ldcg(pp + 1), f, ll);
-            acc = fmaf(__ldcg(pp + 2 + dd), f, acc);
+    const bool has_o = lane * 4 < D;
+    for (int g = warp; g < G; g += kAttWarps) {
+        float mv[kAttMaxSlices], lv[kAttMaxSlices];
+        float4 ov[kAttMaxSlices];
+#pragma unroll
+        for (int s = 0; s < kAttMaxSlices; ++s) {
+            mv[s] = -1.0e30f; lv[s] = 0.0f; ov[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s < slices) {
+                const float* pp = all + ((size_t)s * G + g) * STRIDE;
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(pp));
+                mv[s] = ml.x; lv[s] = ml.y;
+                if (has_o) ov[s] = __ldcg(reinterpret_cast<const float4*>(pp + 4) + lane);
+            }
         }
-        out[g * D + dd] = Act16<BF16>::from_float(ll > 0.0f ? acc / ll : 0.0f);
+        float mm = -1.0e30f;
+#pragma unroll
+        for (int s = 0; s < kAttMaxSlices; ++s) mm = fmaxf(mm, mv[s]);
+        float ll = 0.0f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < kAttMaxSlices; ++s) {
+            const float f = __expf(mv[s] - mm);
+            ll = fmaf(lv[s], f, ll);
+            acc.x = fmaf(ov[s].x, f, acc.x); acc.y = fmaf(ov[s].y, f, acc.y);
+            acc.z = fmaf(ov[s].z, f, acc.z); acc.w = fmaf(ov[s].w, f, acc.w);
+        }
+        if (has_o) {
+            const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+            uint2 packed;
+            T* pe = reinterpret_cast<T*>(&packed);
+            pe[0] = Act16<BF16>::from_float(acc.x * inv); pe[1] = Act16<BF16>::from_float(acc.y * inv);
+            pe[2] = Act16<BF16>::from_float(acc.z * inv); pe[3] = Act16<BF16>::from_float(acc.w * inv);
+            *reinterpret_cast<uint2*>(out + g * D + lane * 4) = packed;
+        }
     }
     if (tid == 0) counters[b * hkv + kvh] = 0;       // ready for the next launch (stream order makes it visible)
 }
@@ -367,7 +399,7 @@ int launch_attention(int group, dim3 grid, cudaStream_t s, const void* q, long l
 
 size_t attention_parts_floats(int batch, int q_heads, int kv_heads, int head_dim, int max_len) {
     const int slices = attention_slices(batch, kv_heads, max_len);
-    return (size_t)batch * q_heads * slices * (head_dim + 2);
+    return (size_t)batch * q_heads * slices * (head_dim + 4);
 }
 
 }  // namespace
@@ -430,8 +462,8 @@ extern "C" int qdec_attention(const void* q, int64_t ldq, const void* kcache, co
     const size_t need = qdec_attention_workspace_bytes(batch, q_heads, kv_heads, head_dim, max_len);
     if (workspace_bytes < need) { set_error("qdec_attention: workspace of %zu bytes required (got %zu)", need, workspace_bytes); return QGEMV_ERR_WORKSPACE; }
     if (reinterpret_cast<uintptr_t>(workspace) % 256 || reinterpret_cast<uintptr_t>(q) % 8 || reinterpret_cast<uintptr_t>(kcache) % 8 ||
-        reinterpret_cast<uintptr_t>(vcache) % 8 || (ldq * 2) % 8) {
-        set_error("qdec_attention: workspace must be 256-byte aligned, q and the caches 8-byte aligned");
+        reinterpret_cast<uintptr_t>(vcache) % 8 || (ldq * 2) % 8 || reinterpret_cast<uintptr_t>(out) % 8 || (ldo * 2) % 8) {
+        set_error("qdec_attention: workspace must be 256-byte aligned, q, out and the caches 8-byte aligned");
         return QGEMV_ERR_ALIGN;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);

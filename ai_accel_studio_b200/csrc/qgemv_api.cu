@@ -128,6 +128,14 @@ MmaPlan choose(const qgemv_problem& p, size_t partial_floats, bool* forced_missi
         if (!pipe.ok) *forced_missing = true;
         return pipe;
     }
+    // Very long rows (14 KB of codes and more, e.g. INT4 with K = 28672) are the one measured case where the
+    // barrier-free variant wins (35.1 against 41.7 us on 8192 x 28672 INT4, M = 1; at half that row length it
+    // loses again, 14.6 against 11.4 us).  Beside 57 KB of staged activations the phased kernel has room for 12 of
+    // its 16 warp rings, the barrier-free one (no run slots, smaller tables) keeps all 16.
+    if (p.kernel == QGEMV_KERNEL_AUTO && p.m == 1 && (long long)p.k_padded * p.bits / 8 >= 14336) {
+        const MmaPlan pipe = plan_pipe(p, plan);
+        if (pipe.ok) return pipe;
+    }
     return plan;
 }
 

@@ -9,6 +9,7 @@ than L2 these are warm-cache latencies -- ``bench.py`` measures the cold, HBM-bo
 
     python -m ai_accel_studio_b200.kernel_suite --m 1 --n 4096 --k 4096 --group-size 64
     python -m ai_accel_studio_b200.kernel_suite --dequant          # the M > 4 path's dequantisation kernel
+    python -m ai_accel_studio_b200.kernel_suite --sweep            # cold-cache size sweep, 4.7 - 117 MB of weights
 """
 from __future__ import annotations
 
@@ -109,15 +110,104 @@ def run_dequant_suite(shapes=((11008, 4096), (4096, 14336), (28672, 8192)), grou
     return rows
 
 
+SWEEP_SHAPES = (
+    # bits, m, n, k, group, outlier columns, residual rank: decoder Linear shapes from 4.7 to 117 MB of weights
+    (2, 1, 4096, 4096, 64, 0, 0), (2, 1, 1024, 4096, 128, 32, 8), (2, 1, 4096, 4096, 128, 32, 8), (4, 1, 4096, 4096, 128, 32, 8),
+    (2, 1, 14336, 4096, 128, 32, 8), (4, 4, 11008, 4096, 128, 32, 8), (4, 1, 14336, 4096, 128, 32, 8), (2, 1, 4096, 14336, 128, 64, 8),
+    (4, 1, 4096, 14336, 128, 64, 8), (2, 1, 28672, 8192, 128, 64, 8), (4, 1, 28672, 8192, 128, 64, 8), (4, 1, 8192, 28672, 128, 64, 8),
+)
+
+
+def algorithmic_bytes(bits, m, n, k, group, oc, rank, bias=False) -> int:
+    """Every operand of one fused GEMV counted once."""
+    b = n * k * bits // 8 + n * (k // group) * 2 + m * k * 2 + m * n * 2
+    if oc:
+        b += n * oc * 2 + oc * 4
+    if rank:
+        b += n * rank * 2 + rank * k * 2
+    return b + (n * 2 if bias else 0)
+
+
+def run_size_sweep(shapes=SWEEP_SHAPES, kernel="auto", peak_gbs=6532.2, ring_bytes=320 << 20, replays=20):
+    """Cold-cache microseconds per fused GEMV over decoder Linear shapes of growing size: for every
+    shape a ring of distinct weight sets larger than 2 x L2 is run back to back from one CUDA graph
+    (the protocol of bench.py), so every launch streams its weights from HBM.  Random codes and scales:
+    timing only.  ``frac`` = algorithmic bytes / time / ``peak_gbs`` (the measured copy bandwidth)."""
+    from . import _cabi, ops
+    if not torch.cuda.is_available():
+        raise RuntimeError("the size sweep requires an NVIDIA CUDA GPU")
+    rows, kern = [], _cabi.KERNEL[kernel]
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for bits, m, n, k, group, oc, rank in shapes:
+        alg = algorithmic_bytes(bits, m, n, k, group, oc, rank)
+        ring = max(4, min(64, -(-ring_bytes // alg)))
+        sets = []
+        for _ in range(ring):
+            sets.append(dict(
+                packed=torch.randint(0, 256, (n, k * bits // 8), dtype=torch.uint8, device="cuda", generator=g),
+                scales=(torch.rand((n, k // group), device="cuda", generator=g) * 0.01 + 0.002).half(),
+                oidx=torch.randperm(k, device="cuda", generator=g)[:oc].to(torch.int32) if oc else None,
+                ow=(torch.randn((n, oc), device="cuda", generator=g) * 0.02).half() if oc else None,
+                ru=(torch.randn((n, rank), device="cuda", generator=g) * 0.02).half() if rank else None,
+                rv=(torch.randn((rank, k), device="cuda", generator=g) * 0.02).half() if rank else None))
+        x = torch.randn((m, k), device="cuda", generator=g).half()
+
+        def one_pass():
+            out = None
+            for w in sets:
+                out = ops.gemv(x, w["packed"], w["scales"], None, w["oidx"], w["ow"], w["ru"], w["rv"], bits, group, k, 0, kern)
+            return out
+        w0 = sets[0]
+        try:
+            plan = ops.plan_describe(x, w0["packed"], w0["scales"], bits, group, k, w0["oidx"], w0["ow"], w0["ru"], w0["rv"], kernel=kern)
+        except _cabi.QgemvError as e:          # a forced kernel this shape cannot use
+            rows.append(dict(bits=bits, m=m, n=n, k=k, group=group, outliers=oc, rank=rank, weight_mb=alg / 1e6, skipped=str(e)))
+            del sets
+            torch.cuda.empty_cache()
+            continue
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                one_pass()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            one_pass()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        for _ in range(replays):
+            graph.replay()
+        en.record()
+        en.synchronize()
+        us = float(st.elapsed_time(en)) * 1e3 / (replays * ring)
+        rows.append(dict(bits=bits, m=m, n=n, k=k, group=group, outliers=oc, rank=rank, weight_mb=alg / 1e6, ring=ring,
+                         us_per_gemv=us, GBps=alg / us / 1e3, frac_of_measured_peak=alg / us / 1e3 / peak_gbs,
+                         kernel=plan.get("name"), grid=plan.get("grid"), tile_aligned=plan.get("tile_aligned")))
+        del sets, graph
+        torch.cuda.empty_cache()
+    return rows
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--dequant", action="store_true", help="time the dequantisation kernel instead of the decode rows")
+    ap.add_argument("--sweep", action="store_true", help="cold-cache size sweep over decoder Linear shapes (4.7 - 117 MB of weights)")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma", "mma_pipe"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--group-size", type=int, default=128)
     ap.add_argument("--repeats", type=int, default=500)
     a = ap.parse_args()
-    rows = run_dequant_suite(group_size=a.group_size) if a.dequant else run_kernel_suite(a.m, a.n, a.k, a.group_size, a.repeats)
+    if a.sweep:
+        rows = run_size_sweep(kernel=a.kernel)
+    elif a.dequant:
+        rows = run_dequant_suite(group_size=a.group_size)
+    else:
+        rows = run_kernel_suite(a.m, a.n, a.k, a.group_size, a.repeats)
     for row in rows:
         print(json.dumps(row))

@@ -14,6 +14,10 @@ from .. import _cabi
 from .groupwise_int2 import GroupwiseInt2Weight, reference_linear
 
 
+_CALLS: dict = {}        # prepared launches of the functional interface (eager calls), see _fused
+_MAX_CALLS = 64
+
+
 def _as_half(t, device):
     if t is None:
         return None
@@ -51,8 +55,24 @@ def _fused(bits, x, pw, bias, outlier_idx, outlier_weight, res_u, res_v, activat
         ru, rv = _as_half(res_u, dev), _as_half(res_v, dev)
     if x.stride(1) != 1:
         x = x.contiguous()
-    return ops.gemv(x, pw.packed, pw.scales, _as_half(bias, dev), oi, ow, ru, rv,
-                    bits, pw.group_size, pw.original_k, act, _cabi.KERNEL[kernel])
+    b16 = _as_half(bias, dev)
+    if torch.compiler.is_compiling():          # the registered operator only where a tracer needs it
+        return ops.gemv(x, pw.packed, pw.scales, b16, oi, ow, ru, rv, bits, pw.group_size, pw.original_k, act,
+                        _cabi.KERNEL[kernel])
+    # Eager: reuse the prepared launch for these operands.  Keyed by addresses AND shapes, so a
+    # recycled address with other dimensions never meets a stale struct.
+    ptr = lambda t: 0 if t is None else t.data_ptr()
+    key = (bits, x.shape[0], x.dtype, x.stride(0), dev, pw.packed.data_ptr(), tuple(pw.packed.shape), pw.packed.stride(0),
+           pw.scales.data_ptr(), tuple(pw.scales.shape), pw.group_size, pw.original_k, ptr(b16), ptr(oi), ptr(ow),
+           0 if oi is None else oi.numel(), ptr(ru), ptr(rv), 0 if ru is None else ru.shape[1], act, kernel)
+    call = _CALLS.get(key)
+    if call is None:
+        if len(_CALLS) >= _MAX_CALLS:
+            _CALLS.clear()
+        call = _CALLS[key] = ops.prepare_call(x, pw.packed, pw.scales, b16, oi, ow, ru, rv, bits, pw.group_size,
+                                              pw.original_k, act, _cabi.KERNEL[kernel], None, key)
+        call.keep = (pw.packed, pw.scales, b16, oi, ow, ru, rv)      # the struct's pointers stay valid while it is cached
+    return call.run(x)
 
 
 def decode_int2_linear(x: torch.Tensor, pw: GroupwiseInt2Weight, bias: torch.Tensor | None = None,

@@ -149,12 +149,11 @@ def _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res
                 raise ValueError(f"{name} must have unit inner stride")
 
 
-@torch.library.custom_op("b200q::gemv", mutates_args=())
-def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
-         outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
-         res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
-         bits: int, group: int, k_original: int, act: int, kernel: int,
-         prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemv_eager(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Optional[torch.Tensor],
+               outlier_idx: Optional[torch.Tensor], outlier_weight: Optional[torch.Tensor],
+               res_u: Optional[torch.Tensor], res_v: Optional[torch.Tensor],
+               bits: int, group: int, k_original: int, act: int, kernel: int,
+               prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[M,N] = act(x . dequant(W)^T + outlier term + low-rank residual + bias), M <= 4
     (``act`` 0 none, 1 ReLU, 2 SiLU; 3 = gated pairs, see ``ACT_SILU_MUL``: y is then [M, N/2]).
 
@@ -176,6 +175,60 @@ def gemv(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, bias: Opti
     with torch.cuda.device(x.device):
         _cabi.run(prob, torch.cuda.current_stream().cuda_stream)
     return y
+
+
+# The registered operator (traceable by Dynamo through its fake kernel) is the same function behind the
+# dispatcher.  Eager callers that do not need tracing call ``gemv_eager`` and save the dispatcher's
+# tens of microseconds per call, which is several times the kernel's own duration.
+gemv = torch.library.custom_op("b200q::gemv", gemv_eager, mutates_args=())
+
+
+class CachedCall:
+    """A module's decode launch with everything that does not change between calls prepared once: the
+    problem struct with the weight pointers filled in, keyed by the shapes and addresses it was built
+    from.  ``run(x)`` then costs an output allocation, three pointer stores and the launch."""
+
+    __slots__ = ("key", "problem", "out_width", "device_index", "keep")
+
+    def __init__(self, key, problem, out_width, device_index):
+        self.key, self.problem, self.out_width, self.device_index = key, problem, out_width, device_index
+        self.keep = None                      # tensors the struct points at, when the caller does not hold them itself
+
+    def run(self, x: torch.Tensor) -> torch.Tensor:
+        import ctypes
+        idx = self.device_index
+        y = torch.empty((x.shape[0], self.out_width), dtype=x.dtype, device=x.device)
+        stream = torch.cuda.current_stream(idx)
+        handle = stream.cuda_stream
+        ws = _WORKSPACE.get((idx, handle))
+        if ws is None:
+            ws = ensure_workspace(x.device, stream)
+        p = self.problem
+        p.x, p.y, p.workspace = x.data_ptr(), y.data_ptr(), ws.data_ptr()
+        if torch.cuda.current_device() == idx:
+            rc = _cabi.lib().qgemv_run(ctypes.byref(p), handle)
+        else:
+            with torch.cuda.device(idx):
+                rc = _cabi.lib().qgemv_run(ctypes.byref(p), handle)
+        if rc != 0:
+            _cabi.check(rc)
+        return y
+
+
+def prepare_call(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits, group, k_original, act, kernel,
+                 prefetch=None, key=None) -> CachedCall:
+    """Validate once and build a ``CachedCall`` for activations shaped and strided like ``x``."""
+    _check_gemv_inputs(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, bits)
+    if outlier_idx is not None and outlier_idx.numel() == 0:
+        outlier_idx = outlier_weight = None
+    if res_u is not None and res_u.numel() == 0:
+        res_u = res_v = None
+    ws = ensure_workspace(x.device)
+    width = _out_width(packed, act)
+    y = torch.empty((x.shape[0], width), dtype=x.dtype, device=x.device)
+    prob = _problem(x, packed, scales, bias, outlier_idx, outlier_weight, res_u, res_v, y, ws, bits, group, k_original, act,
+                    kernel, prefetch)
+    return CachedCall(key, prob, width, _device_index(x.device))
 
 
 @gemv.register_fake

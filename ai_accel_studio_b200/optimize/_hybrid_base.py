@@ -156,6 +156,24 @@ class HybridPackedLinear(nn.Module):
 
     def _fused(self, xp: torch.Tensor) -> torch.Tensor:
         from .. import _cabi, ops
+        if not torch.compiler.is_compiling():
+            # eager: the prepared launch of this module for activations of this shape (rebuilt whenever a
+            # buffer has moved or a setting has changed)
+            pre = self.prefetch_next
+            key = (xp.shape[0], xp.dtype, xp.stride(0), xp.device, self.packed.data_ptr(), self.scales.data_ptr(),
+                   self.outlier_weight.data_ptr(), self.residual_rank, 0 if self.res_u is None else self.res_u.data_ptr(),
+                   0 if self.bias is None else self.bias.data_ptr(), self.kernel, getattr(self, "debug", 0), self.gated_pairs,
+                   0 if pre is None else pre.data_ptr())
+            call = self.__dict__.get("_call")
+            if call is None or call.key != key:
+                has_o = self.outlier_idx.numel() > 0
+                call = ops.prepare_call(xp, self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
+                                        self.outlier_weight if has_o else None,
+                                        self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
+                                        self.bits, self.group_size, self.original_k, 3 if self.gated_pairs else 0,
+                                        self._kernel_code(), pre, key)
+                self.__dict__["_call"] = call
+            return call.run(xp)
         return ops.gemv(xp, self.packed, self.scales, self.bias, self.outlier_idx if self.outlier_idx.numel() else None,
                         self.outlier_weight if self.outlier_idx.numel() else None,
                         self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,

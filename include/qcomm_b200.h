@@ -9,7 +9,7 @@
  * ranks compute bit-identical sums.  Two buffer halves alternate from call to call; a rank cannot
  * run two calls ahead of another, so nothing is overwritten while it is still being read.
  *
- * Peer loads and stores only: no switch multicast, no library kernel is handed a peer pointer.
+ * Peer loads and stores only: no in-switch reduction or broadcast, no library kernel is handed a peer pointer.
  * The reference project has no multi-GPU path, so nothing here has a counterpart in it; the
  * contract is the all-reduce of a Megatron-style K-split Linear.
  *

@@ -48,8 +48,9 @@ enum qgemv_dtype { QGEMV_F16 = 0, QGEMV_BF16 = 1, QGEMV_F32 = 2 };
  * tile phase) when the shape allows it and the CUDA-core kernel otherwise; SIMT and MMA force one
  * of the two.  MMA_PIPE asks for the barrier-free variant of the tensor-core kernel (whole 16-row
  * tiles per CTA, per-tile arrival counters instead of the CTA barrier); it is measured slower than
- * MMA on every benchmark shape (13.7 against 10.4 us on the headline one) and is kept for A/B
- * measurements and as the base of further work, never chosen by AUTO.  A forced kernel that the
+ * MMA on the benchmark shapes (13.7 against 10.4 us on the headline one) and is kept for A/B
+ * measurements and as the base of further work; AUTO takes it only for M = 1 with rows of 14 KB of
+ * codes or more, the one case where it measured faster.  A forced kernel that the
  * shape does not allow returns QGEMV_ERR_SHAPE. */
 enum qgemv_kernel { QGEMV_KERNEL_AUTO = 0, QGEMV_KERNEL_SIMT = 1, QGEMV_KERNEL_MMA = 2, QGEMV_KERNEL_MMA_PIPE = 3 };
 

@@ -158,6 +158,31 @@ def test_pipelined_kernel_variants(bits, m, n, k, group, oc, rank, coracle):
     assert out.value == 0
 
 
+def test_planner_takes_the_barrier_free_kernel_for_very_long_rows(coracle):
+    """M = 1 and 14 KB of codes per row (INT4, K = 28672): the one shape class where the barrier-free kernel
+    measured faster, so the planner picks it; checked against the oracle like every other path."""
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    bits, m, n, k, group, oc, rank = 4, 1, 4096, 28672, 128, 64, 8
+    h, d = _case(bits, m, n, k, group, oc, rank, seed=5)
+    ws = _workspace()
+    y = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    p = _problem(bits, m, n, k, group, oc, rank, d, y, ws)
+    info = _cabi.plan_describe(p)
+    assert info.variant == 2 and info.warps == 16
+    for _ in range(2):
+        assert lib.qgemv_run(ctypes.byref(p), ctypes.c_void_p(stream)) == 0, _cabi.last_error()
+    torch.cuda.synchronize()
+    assert_within_tolerance(y.float().cpu().numpy(), _oracle(coracle, bits, k, group, h), "barrier-free kernel by the planner's choice")
+    p2 = _problem(bits, 2, n, k, group, oc, rank, d, y, ws)                  # two rows: the phased kernel
+    p2.x = torch.zeros((2, k), dtype=torch.float16, device="cuda").data_ptr()
+    assert _cabi.plan_describe(p2).variant == 1
+    out = ctypes.c_int32(-1)
+    assert lib.qgemv_workspace_status(ws.data_ptr(), ctypes.c_void_p(stream), ctypes.byref(out)) == 0
+    torch.cuda.synchronize()
+    assert out.value == 0
+
+
 @pytest.mark.parametrize("kernel", ["auto", "mma_pipe", "simt"])
 def test_chain_of_dependent_launches(kernel):
     """x_{i+1} = y_i through 12 square GEMVs issued back to back: every launch is allowed to start
