@@ -20,7 +20,7 @@ ABI_VERSION = 4
 
 EXPORTS = ("qgemv_run", "qgemv_run_static", "qgemv_plan_launches", "qgemv_plan_describe", "qgemv_workspace_status", "qgemv_workspace_bytes", "qgemv_plan_name", "qdequant", "qunpack_codes",
            "qgemv_error_string", "qgemv_abi_version", "qgemv_sizeof_problem",
-           "qcomm_slot_bytes", "qcomm_flag_bytes", "qcomm_state_bytes", "qcomm_allreduce", "qcomm_status", "qcomm_alloc", "qcomm_free",
+           "qcomm_slot_bytes", "qcomm_flag_bytes", "qcomm_state_bytes", "qcomm_allreduce", "qcomm_allreduce_rmsnorm", "qcomm_status", "qcomm_alloc", "qcomm_free",
            "qcomm_ipc_export", "qcomm_ipc_open", "qcomm_ipc_close",
            "qdec_rmsnorm", "qdec_rope_append", "qdec_attention_workspace_bytes", "qdec_attention", "qdec_silu_mul")
 COMM_MAX_RANKS, COMM_MAX_BLOCKS, COMM_IPC_HANDLE_BYTES = 8, 64, 64
@@ -102,6 +102,9 @@ def lib():
     l.qcomm_state_bytes.restype = C.c_size_t
     l.qcomm_allreduce.argtypes = [C.POINTER(CommGroup), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     l.qcomm_allreduce.restype = C.c_int
+    l.qcomm_allreduce_rmsnorm.argtypes = [C.POINTER(CommGroup), C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                          C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    l.qcomm_allreduce_rmsnorm.restype = C.c_int
     l.qcomm_status.argtypes = [C.POINTER(CommGroup), C.c_void_p, C.POINTER(C.c_int32)]
     l.qcomm_status.restype = C.c_int
     l.qcomm_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]

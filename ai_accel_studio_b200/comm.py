@@ -91,6 +91,29 @@ class OneShotAllReduce:
                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return t
 
+    def fits_rows(self, partial: torch.Tensor) -> bool:
+        return (partial.is_cuda and partial.dtype in _DT and partial.ndim == 2 and partial.stride(1) == 1
+                and partial.shape[1] % 8 == 0 and partial.shape[1] <= 16384 and partial.shape[0] <= _cabi.COMM_MAX_BLOCKS
+                and partial.numel() <= self.max_elems and partial.data_ptr() % 16 == 0 and partial.stride(0) % 8 == 0)
+
+    def allreduce_rmsnorm(self, partial: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """One kernel for "all-reduce the K-split projection's partial result, add it to the residual stream,
+        RMS-normalise": ``h += sum over ranks of partial`` in place, returns ``rmsnorm(h) * weight``.  ``partial`` and
+        ``h``: ``[rows, hidden]``; counts as one call of the group's sequence, so every rank must make it."""
+        if not self.fits_rows(partial):
+            raise ValueError("partial does not fit the fused all-reduce (fp16/bf16 [rows, hidden], unit inner stride, 16-byte "
+                             f"aligned rows, hidden a multiple of 8, at most {self.max_elems} elements)")
+        if h.shape != partial.shape or h.dtype != partial.dtype or h.stride(1) != 1 or weight.dtype != h.dtype or \
+                weight.numel() != h.shape[1] or not weight.is_contiguous():
+            raise ValueError("h must match partial and weight must be a contiguous [hidden] tensor of the same dtype")
+        y = torch.empty(h.shape, dtype=h.dtype, device=h.device)
+        with torch.cuda.device(h.device):
+            _cabi.check(self.lib.qcomm_allreduce_rmsnorm(C.byref(self.g), C.c_void_p(partial.data_ptr()), partial.stride(0),
+                                                         C.c_void_p(h.data_ptr()), h.stride(0), C.c_void_p(weight.data_ptr()),
+                                                         C.c_void_p(y.data_ptr()), y.stride(0), h.shape[0], h.shape[1], float(eps),
+                                                         _DT[h.dtype], C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return y
+
     def status(self) -> int:
         """Read and clear the status word (synchronises the current stream): 0, or 1 if a wait for a peer ran out."""
         out = C.c_int32(-1)

@@ -103,10 +103,193 @@ __global__ void __launch_bounds__(kCommThreads) qcomm_allreduce_kernel(const Com
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// all-reduce + residual update + RMS normalisation: one CTA per row
+// ---------------------------------------------------------------------------------------------
+constexpr int kFusedThreads = 256;
+constexpr int kFusedMaxVec = 8;                   // 8-element vectors per thread: hidden <= 256 * 8 * 8
+
+struct FusedArgs {
+    CommArgs c;
+    const void* partial; long long ldp;
+    void* h; long long ldh;
+    const void* weight;
+    void* y; long long ldy;
+    int hidden;
+    float eps;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(kFusedThreads) qcomm_allreduce_rmsnorm_kernel(const FusedArgs a) {
+    using T = typename Act16<BF16>::T;
+    const CommArgs& c = a.c;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int tid = threadIdx.x, row = blockIdx.x, nvec = a.hidden >> 3;
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // the producer of `partial` (and of h) has finished
+    const unsigned call = ld_relaxed_gpu(c.state);
+    const unsigned half = call & 1u, tag = call + 1u;
+    const size_t half_elems = (size_t)c.world * c.max_elems;
+    const size_t row_off = (size_t)row * a.hidden;
+    __shared__ float red[kFusedThreads / 32];
+    __shared__ float total;
+
+    // 1. this rank's partial row into its slot of every rank's receive buffer
+    const T* part = static_cast<const T*>(a.partial) + (size_t)row * a.ldp;
+#pragma unroll
+    for (int i = 0; i < kFusedMaxVec; ++i) {
+        const int v = tid + i * kFusedThreads;
+        if (v < nvec) {
+            const uint4 mine = *reinterpret_cast<const uint4*>(part + v * 8);
+            for (int p = 0; p < c.world; ++p) {
+                const int peer = (c.rank + p) % c.world;
+                T* dst = reinterpret_cast<T*>(c.slots[peer]) + half * half_elems + (size_t)c.rank * c.max_elems + row_off + v * 8;
+                *reinterpret_cast<uint4*>(dst) = mine;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. flags: raise mine for this row at every rank, wait (bounded) for everybody's here
+    if (tid < c.world) {
+        st_release_sys(c.flags[tid] + (half * c.world + c.rank) * QCOMM_MAX_BLOCKS + row, tag);
+        const unsigned* f = c.flags[c.rank] + (half * c.world + tid) * QCOMM_MAX_BLOCKS + row;
+        int probes = 0;
+        while (ld_acquire_sys(f) != tag) {
+            if (++probes > c.wait_limit) { atomicExch(c.state + 2, 1u); break; }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    // 3. sum of the slots in rank order, rounded; residual update; sum of squares
+    T* h = static_cast<T*>(a.h) + (size_t)row * a.ldh;
+    const T* base = reinterpret_cast<const T*>(c.slots[c.rank]) + half * half_elems + row_off;
+    float f[kFusedMaxVec][8];
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kFusedMaxVec; ++i) {
+        const int v = tid + i * kFusedThreads;
+        if (v < nvec) {
+            float acc[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[q] = 0.0f;
+            for (int r = 0; r < c.world; ++r) {
+                const uint4 sv = ld_cg_u128(base + (size_t)r * c.max_elems + v * 8);
+                const T* e = reinterpret_cast<const T*>(&sv);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) acc[q] += Act16<BF16>::to_float(e[q]);
+            }
+            const uint4 hv = *reinterpret_cast<const uint4*>(h + v * 8);
+            const T* he = reinterpret_cast<const T*>(&hv);
+            uint4 ov;
+            T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float d = Act16<BF16>::to_float(Act16<BF16>::from_float(acc[q]));
+                oe[q] = Act16<BF16>::from_float(Act16<BF16>::to_float(he[q]) + d);
+                f[i][q] = Act16<BF16>::to_float(oe[q]);
+                sq = fmaf(f[i][q], f[i][q], sq);
+            }
+            *reinterpret_cast<uint4*>(h + v * 8) = ov;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((tid & 31) == 0) red[tid >> 5] = sq;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kFusedThreads / 32; ++i) t += red[i];
+        total = rsqrtf(t / (float)a.hidden + a.eps);
+        // 5. the last CTA of the launch advances the call counter (every CTA has read it by now)
+        const unsigned old = atomicAdd(c.state + 1, 1u);
+        if (old == gridDim.x - 1) {
+            c.state[1] = 0u;
+            __threadfence();
+            c.state[0] = tag;
+        }
+    }
+    __syncthreads();
+    // 4. normalise
+    const float inv = total;
+    const T* w = static_cast<const T*>(a.weight);
+    T* y = static_cast<T*>(a.y) + (size_t)row * a.ldy;
+#pragma unroll
+    for (int i = 0; i < kFusedMaxVec; ++i) {
+        const int v = tid + i * kFusedThreads;
+        if (v < nvec) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + v * 8);
+            const T* we = reinterpret_cast<const T*>(&wv);
+            uint4 ov;
+            T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                oe[q] = Act16<BF16>::from_float(Act16<BF16>::to_float(we[q]) *
+                                                Act16<BF16>::to_float(Act16<BF16>::from_float(f[i][q] * inv)));
+            *reinterpret_cast<uint4*>(y + v * 8) = ov;
+        }
+    }
+}
+
+// Validate a group and fill the device-side view of it.
+int fill_comm_args(const qcomm_group* g, const char* who, CommArgs& c) {
+    if (!g) { set_error("%s: group is NULL", who); return QGEMV_ERR_BAD_ARG; }
+    if (g->world < 1 || g->world > QCOMM_MAX_RANKS || g->rank < 0 || g->rank >= g->world) {
+        set_error("%s: bad rank %d / world %d (at most %d ranks)", who, g->rank, g->world, QCOMM_MAX_RANKS);
+        return QGEMV_ERR_BAD_ARG;
+    }
+    if (g->max_elems % 8) { set_error("%s: max_elems must be a multiple of 8", who); return QGEMV_ERR_SHAPE; }
+    if (!g->state) { set_error("%s: state is NULL", who); return QGEMV_ERR_BAD_ARG; }
+    for (int r = 0; r < g->world; ++r) {
+        if (!g->slots[r] || !g->flags[r]) { set_error("%s: slots / flags of rank %d are NULL", who, r); return QGEMV_ERR_BAD_ARG; }
+        c.slots[r] = static_cast<unsigned char*>(g->slots[r]);
+        c.flags[r] = static_cast<unsigned*>(g->flags[r]);
+    }
+    c.state = static_cast<unsigned*>(g->state);
+    c.rank = g->rank; c.world = g->world; c.max_elems = g->max_elems;
+    c.wait_limit = g->wait_limit > 0 ? g->wait_limit : kDefaultWaitLimit;
+    return QGEMV_OK;
+}
+
 }  // namespace
 }  // namespace qgemv
 
 using namespace qgemv;
+
+extern "C" int qcomm_allreduce_rmsnorm(const qcomm_group* g, const void* partial, int64_t ldp, void* h, int64_t ldh,
+                                       const void* weight, void* y, int64_t ldy, int rows, int hidden, float eps,
+                                       int dtype, void* stream) {
+    FusedArgs a{};
+    const int rc = fill_comm_args(g, "qcomm_allreduce_rmsnorm", a.c);
+    if (rc != QGEMV_OK) return rc;
+    if (!partial || !h || !weight || !y) { set_error("qcomm_allreduce_rmsnorm: null pointer"); return QGEMV_ERR_BAD_ARG; }
+    if (dtype != QGEMV_F16 && dtype != QGEMV_BF16) { set_error("qcomm_allreduce_rmsnorm: dtype must be fp16 or bf16"); return QGEMV_ERR_BAD_ARG; }
+    if (rows < 1 || rows > QCOMM_MAX_BLOCKS) { set_error("qcomm_allreduce_rmsnorm: 1..%d rows (got %d)", QCOMM_MAX_BLOCKS, rows); return QGEMV_ERR_TOO_LARGE; }
+    if (hidden < 8 || hidden % 8 || hidden > kFusedThreads * kFusedMaxVec * 8) { set_error("qcomm_allreduce_rmsnorm: hidden=%d must be a multiple of 8, at most %d", hidden, kFusedThreads * kFusedMaxVec * 8); return QGEMV_ERR_SHAPE; }
+    if ((int64_t)rows * hidden > g->max_elems) { set_error("qcomm_allreduce_rmsnorm: %d x %d elements exceed the slot capacity of %d", rows, hidden, g->max_elems); return QGEMV_ERR_TOO_LARGE; }
+    if (ldp < hidden || ldh < hidden || ldy < hidden) { set_error("qcomm_allreduce_rmsnorm: a leading dimension is smaller than hidden"); return QGEMV_ERR_SHAPE; }
+    if (reinterpret_cast<uintptr_t>(partial) % 16 || reinterpret_cast<uintptr_t>(h) % 16 || reinterpret_cast<uintptr_t>(y) % 16 ||
+        reinterpret_cast<uintptr_t>(weight) % 16 || ldp % 8 || ldh % 8 || ldy % 8) {
+        set_error("qcomm_allreduce_rmsnorm: rows must be 16-byte aligned");
+        return QGEMV_ERR_ALIGN;
+    }
+    a.partial = partial; a.ldp = ldp; a.h = h; a.ldh = ldh; a.weight = weight; a.y = y; a.ldy = ldy;
+    a.hidden = hidden; a.eps = eps;
+    a.c.data = nullptr; a.c.elems = rows * hidden;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows);
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = dtype == QGEMV_BF16 ? cudaLaunchKernelEx(&cfg, qcomm_allreduce_rmsnorm_kernel<true>, a)
+                                              : cudaLaunchKernelEx(&cfg, qcomm_allreduce_rmsnorm_kernel<false>, a);
+    (void)e;
+    return check_launch("qcomm_allreduce_rmsnorm_kernel");
+}
 
 extern "C" size_t qcomm_slot_bytes(int world, int max_elems) { return (size_t)2 * world * max_elems * 2; }
 extern "C" size_t qcomm_flag_bytes(int world) { return (size_t)2 * world * QCOMM_MAX_BLOCKS * sizeof(unsigned); }

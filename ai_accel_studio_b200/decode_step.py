@@ -175,26 +175,82 @@ class NativeDecodeStep:
         hq = max(int(getattr(l.self_attn.q_proj, "out_features")) // self.head_dim for l in self.layers)
         hkv = min(k.shape[1] for k, _ in self.kv)
         self.att_ws = attention_workspace(self.batch, hq, hkv, self.head_dim, self.max_len, self.device)
+        # Side streams for projections that read the same activations and are separate launches (k and v beside q
+        # when their bit widths differ): each gets its own GEMV scratch buffer now, before any graph capture.
+        self.side = [torch.cuda.Stream(device=self.device) for _ in range(2)]
+        from . import ops
+        for s in self.side:
+            ops.ensure_workspace(self.device, s)
+
+    # Launch the k and v projections on side streams beside q when the three are separate modules: their grids are
+    # small (one CTA per 16-row tile), so they run next to each other instead of one after the other.
+    parallel_kv = False
+
+    def _qkv(self, attn, x):
+        from .optimize._hybrid_base import HybridPackedLinear
+        mods = (attn.q_proj, attn.k_proj, attn.v_proj)
+        if not NativeDecodeStep.parallel_kv or not all(isinstance(m, (HybridPackedLinear, nn.Linear)) for m in mods):
+            return attn.q_proj(x), attn.k_proj(x), attn.v_proj(x)
+        main = torch.cuda.current_stream(self.device)
+        outs = [None, None]
+        for i, (s, m) in enumerate(zip(self.side, (attn.k_proj, attn.v_proj))):
+            s.wait_stream(main)                                  # x is ready
+            with torch.cuda.stream(s):
+                outs[i] = m(x)
+        q = attn.q_proj(x)
+        for s, o in zip(self.side, outs):
+            main.wait_stream(s)
+            o.record_stream(main)                                # consumed on the main stream: not to be recycled before that
+        x.record_stream(self.side[0])
+        x.record_stream(self.side[1])
+        return q, outs[0], outs[1]
+
+    # Fuse the all-reduce of the K-split projections into the normalisation that consumes their result
+    # (comm.OneShotAllReduce.allreduce_rmsnorm) when tensor parallelism runs on the one-shot buffers.
+    fuse_reduce = False
+
+    @staticmethod
+    def _project(linear, x):
+        """A K-split projection that would all-reduce its result hands back its partial sum when the group's one-shot
+        buffers can take it: the reduction is then fused into the normalisation that consumes it."""
+        from .tp import AllReduceLinear
+        if isinstance(linear, AllReduceLinear) and not AllReduceLinear.skip_collective:
+            comm = AllReduceLinear.one_shot
+            if NativeDecodeStep.fuse_reduce and comm is not None and comm.world > 1:
+                y = linear.inner(x)
+                if comm.fits_rows(y):
+                    return y, comm
+                if comm.fits(y):
+                    return comm(y), None
+                torch.distributed.all_reduce(y, group=linear.group)
+                return y, None
+        return linear(x), None
+
+    @staticmethod
+    def _norm(h, delta, comm, norm):
+        if comm is not None:
+            return comm.allreduce_rmsnorm(delta, h, norm.weight, norm.variance_epsilon)
+        return rmsnorm(h, delta, norm.weight, norm.variance_epsilon)
 
     @torch.no_grad()
     def step(self, tok: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         inner, d = self.inner, self.head_dim
         h = inner.embed_tokens(tok).reshape(self.batch, -1).contiguous()
-        delta = None
+        delta = comm = None
         for i, layer in enumerate(self.layers):
             attn, mlp = layer.self_attn, layer.mlp
-            x = rmsnorm(h, delta, layer.input_layernorm.weight, layer.input_layernorm.variance_epsilon)
-            q, k, v = attn.q_proj(x), attn.k_proj(x), attn.v_proj(x)
+            x = self._norm(h, delta, comm, layer.input_layernorm)
+            q, k, v = self._qkv(attn, x)
             kc, vc = self.kv[i]
             rope_append(q, k, v, self.cos, self.sin, pos, kc, vc, d, self.status)
             a = attention(q, kc, vc, pos, float(getattr(attn, "scaling", d ** -0.5)), self.att_ws)
-            delta = attn.o_proj(a)
-            x = rmsnorm(h, delta, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.variance_epsilon)
+            delta, comm = self._project(attn.o_proj, a)
+            x = self._norm(h, delta, comm, layer.post_attention_layernorm)
             if type(mlp).__name__ == "GatedFeedForward":
-                delta = mlp(x)
+                delta, comm = self._project(mlp.down_proj, mlp.gate_up(x))
             else:
-                delta = mlp.down_proj(silu_mul(mlp.gate_proj(x), mlp.up_proj(x)))
-        x = rmsnorm(h, delta, inner.norm.weight, inner.norm.variance_epsilon)
+                delta, comm = self._project(mlp.down_proj, silu_mul(mlp.gate_proj(x), mlp.up_proj(x)))
+        x = self._norm(h, delta, comm, inner.norm)
         return self.model.lm_head(x)
 
     def check_status(self) -> int:

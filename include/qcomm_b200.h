@@ -56,6 +56,19 @@ size_t qcomm_state_bytes(void);
  * anyway, with whatever the slot holds, and raises the status word. */
 int qcomm_allreduce(const qcomm_group* g, void* data, int64_t elems, int dtype, void* stream);
 
+/* The all-reduce fused with the step that follows it in a decoder layer -- residual update and RMS
+ * normalisation -- as ONE kernel (one CTA per row):
+ *     d[m, :]  = r(sum over ranks of their partial[m, :])      (rounded as a separate all-reduce would store it)
+ *     h[m, :] <- r(h[m, :] + d[m, :])                          (in place)
+ *     y[m, :]  = r(weight[:] * r(h[m, :] * rsqrt(mean(h[m, :]^2) + eps)))
+ * partial: this rank's [rows, hidden] partial result of a K-split projection (leading dimension ldp);
+ * h, y, weight as in qdec_rmsnorm (qdecode_b200.h).  rows <= QCOMM_MAX_BLOCKS, hidden a multiple of 8
+ * and at most 16384, rows * hidden <= max_elems, all rows 16-byte aligned.  Counts as one call of
+ * the group's call sequence, like qcomm_allreduce; same waiting and status behaviour. */
+int qcomm_allreduce_rmsnorm(const qcomm_group* g, const void* partial, int64_t ldp, void* h, int64_t ldh,
+                            const void* weight, void* y, int64_t ldy, int rows, int hidden, float eps,
+                            int dtype, void* stream);
+
 /* Enqueue a copy of the status word into *host_out (0 = every call so far completed; 1 = a wait for
  * a peer ran out) and reset it; synchronise `stream` before reading. */
 int qcomm_status(const qcomm_group* g, void* stream, int32_t* host_out);

@@ -56,6 +56,50 @@ def test_single_rank_group_is_the_identity_and_graph_capturable():
     comm.close()
 
 
+def test_fused_allreduce_rmsnorm_single_rank_equals_the_plain_kernels():
+    """World 1: the fused kernel must do exactly what rmsnorm(h, delta) does, eagerly and from a graph, and
+    count as one call of the group's sequence (a plain all-reduce after it still works)."""
+    from ai_accel_studio_b200 import decode_step as ds
+    keep = _buffers(1, 4 * 8192)
+    comm = OneShotAllReduce(rank=0, world=1, max_elems=4 * 8192, peers=[(keep[0].data_ptr(), keep[1].data_ptr())])
+    torch.manual_seed(4)
+    for dt in (torch.float16, torch.bfloat16):
+        for rows, hidden in ((1, 4096), (4, 8192), (2, 896)):
+            h = (torch.randn(rows, hidden) * 2).to(dt).cuda()
+            part = torch.randn(rows, hidden).to(dt).cuda()
+            w = (1 + 0.1 * torch.randn(hidden)).to(dt).cuda()
+            h_ref = h.clone()
+            y_ref = ds.rmsnorm(h_ref, part, w, 1e-5)
+            for _ in range(3):                                       # both buffer halves
+                h_got = h.clone()
+                y_got = comm.allreduce_rmsnorm(part, h_got, w, 1e-5)
+                assert torch.equal(h_got, h_ref) and torch.equal(y_got, y_ref), (dt, rows, hidden)
+    v = torch.randn(4096, device="cuda").half()
+    v2 = v.clone()
+    comm(v2)
+    assert torch.equal(v, v2)
+    h = torch.randn(1, 4096, device="cuda").half()
+    part, w = torch.randn(1, 4096, device="cuda").half(), torch.ones(4096, device="cuda").half()
+    static_h = h.clone()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        comm.allreduce_rmsnorm(part, static_h, w, 1e-5)
+    torch.cuda.current_stream().wait_stream(s)
+    static_h.copy_(h)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y = comm.allreduce_rmsnorm(part, static_h, w, 1e-5)
+    g.replay()
+    torch.cuda.synchronize()
+    h_ref = h.clone()
+    assert torch.equal(y, ds.rmsnorm(h_ref, part, w, 1e-5)) and torch.equal(static_h, h_ref) and comm.status() == 0
+    with pytest.raises(ValueError):
+        comm.allreduce_rmsnorm(torch.zeros(8, 8192, device="cuda").half(), torch.zeros(8, 8192, device="cuda").half(),
+                               torch.ones(8192, device="cuda").half(), 1e-5)      # 8 x 8192 elements exceed a slot
+    comm.close()
+
+
 def test_two_ranks_in_turns_and_the_wait_that_runs_out():
     world, n = 2, 8192
     bufs = [_buffers(world, n) for _ in range(world)]
@@ -101,6 +145,22 @@ def _two_gpu_rank(rank, world, port, ret):
                     y = x.clone()
                     comm(y)
                     ok = ok and bool(torch.equal(y, want))
+        # the all-reduce fused with the residual update and RMS norm against NCCL + the plain kernels
+        from ai_accel_studio_b200 import decode_step as ds
+        for rows, hidden in ((1, 8192), (4, 4096), (2, 896)):
+            for dt in (torch.float16, torch.bfloat16):
+                for _ in range(10):
+                    part = torch.randn((rows, hidden), generator=g, device="cuda").to(dt)
+                    h = torch.randn((rows, hidden), generator=torch.Generator(device="cuda").manual_seed(7), device="cuda").to(dt)
+                    w = torch.ones(hidden, device="cuda").to(dt)
+                    every = [torch.empty_like(part) for _ in range(world)]
+                    dist.all_gather(every, part)
+                    delta = sum(e.float() for e in every).to(dt)
+                    h_ref = h.clone()
+                    y_ref = ds.rmsnorm(h_ref, delta, w, 1e-6)
+                    h_got = h.clone()
+                    y_got = comm.allreduce_rmsnorm(part, h_got, w, 1e-6)
+                    ok = ok and bool(torch.equal(h_got, h_ref)) and bool(torch.equal(y_got, y_ref))
         # captured in a graph together with a producer kernel
         static = torch.zeros(8192, device="cuda").half()
         src = torch.randn(8192, generator=g, device="cuda").half()
