@@ -42,8 +42,8 @@ def main():
     ap.add_argument("--framework-step", action="store_true",
                     help="run the work between the GEMVs (norms, rotary embedding, attention, SwiGLU) with the framework's "
                          "operators instead of this package's decode-step kernels")
-    ap.add_argument("--parallel-kv", action="store_true",
-                    help="launch the k and v projections on side streams beside q where the three are separate launches")
+    ap.add_argument("--serial-kv", action="store_true",
+                    help="do not launch the k and v projections on side streams beside q where the three are separate launches")
     ap.add_argument("--fused-reduce", action="store_true",
                     help="tensor parallel: fuse every all-reduce into the RMS normalisation that consumes its result")
     ap.add_argument("--nccl-all-reduce", action="store_true",
@@ -60,10 +60,10 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    if a.fused_reduce or a.parallel_kv:
+    if a.fused_reduce or a.serial_kv:
         from ai_accel_studio_b200.decode_step import NativeDecodeStep
         NativeDecodeStep.fuse_reduce = a.fused_reduce
-        NativeDecodeStep.parallel_kv = a.parallel_kv
+        NativeDecodeStep.parallel_kv = not a.serial_kv
     for variant in a.variants:
         res = mt.decode_benchmark(a.shape, dev, a.batch, a.prompt, a.new, tuple(a.probs), variant == "mixed", world,
                                   a.layers, use_cuda_graph=not a.no_graph, compile_layers=a.compile_layers,

@@ -40,8 +40,8 @@ def ensure_workspace(device, stream=None) -> torch.Tensor:
     """The scratch buffer of ``stream`` (default: the current stream) on ``device``; zero-filled once.
 
     The first call for a device, which allocates that device's pool, must come before any CUDA-graph
-    capture starts.  Later calls never allocate unless more than ``_POOL_SIZE`` streams of one device
-    have issued GEMVs, and then only outside a capture.  Calls issued on one stream are ordered, so
+    capture starts.  Calls outside a capture keep ``_POOL_SIZE`` spare buffers ready, so up to that many
+    streams may issue their first GEMV inside one capture without any allocation.  Calls issued on one stream are ordered, so
     they share a workspace; calls on different streams get different ones and may overlap freely."""
     device = torch.device(device)
     if device.type != "cuda":
@@ -64,6 +64,9 @@ def ensure_workspace(device, stream=None) -> torch.Tensor:
                                "during a CUDA-graph capture: call ensure_workspace(device, stream) for it before capturing")
         pool.append(_new_workspace(idx))
     ws = _WORKSPACE[(idx, handle)] = pool.pop()
+    if not capturing:
+        while len(pool) < _POOL_SIZE:          # keep spares for streams that first appear inside a capture
+            pool.append(_new_workspace(idx))
     return ws
 
 

@@ -136,12 +136,14 @@ SHAPES = {
 }
 
 
+@pytest.mark.parametrize("side_streams", [True, False])
 @pytest.mark.parametrize("shape,batch,fuse", [("llama-like", 1, False), ("llama-like", 2, True), ("qwen-like", 1, False),
                                               ("wide-heads", 3, True)])
-def test_native_step_tracks_the_framework_forward(monkeypatch, shape, batch, fuse):
+def test_native_step_tracks_the_framework_forward(monkeypatch, shape, batch, fuse, side_streams):
     """Same model, same prompt, two static caches: at every step both paths get the same token and
     position; logits, and the keys / values appended to the caches, must agree to rounding."""
     monkeypatch.setitem(mt.SHAPES, shape, SHAPES[shape])
+    monkeypatch.setattr(ds.NativeDecodeStep, "parallel_kv", side_streams)      # k / v beside q on side streams, or one after the other
     dev = torch.device("cuda")
     model = mt.build_fp16_model(shape, dev)
     probs = (0.0, 1.0, 0.0) if fuse else (0.5, 0.4, 0.1)                         # one bit width: every sibling set can merge
