@@ -1,4 +1,5 @@
-// One-shot all-reduce of small 16-bit vectors over peer memory: see include/qcomm_b200.h.
+// One-shot all-reduce of small 16-bit vectors over peer memory (self-validating words), and the same
+// collective fused with the residual update and RMS norm that follow it: see include/qcomm_b200.h.
 #include <cstring>
 
 #include "qgemv_common.cuh"
@@ -35,6 +36,21 @@ __device__ __forceinline__ unsigned ld_relaxed_gpu(const unsigned* p) {
     unsigned v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
 }
 
+// Bytes of the plain receive area (used by the fused all-reduce + RMS norm kernel with its flags) and of the
+// self-validating area behind it (used by qcomm_allreduce): [2 halves][world][max_elems / 2] words of 8 bytes,
+// each {two 16-bit elements, 32-bit call tag}.
+__host__ __device__ inline size_t plain_bytes(int world, int max_elems) { return (size_t)2 * world * max_elems * 2; }
+
+__device__ __forceinline__ void st_relaxed_sys_v2(unsigned long long* p, unsigned long long a, unsigned long long b) {
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_sys_v2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+// One-shot all-reduce with self-validating words: every 8-byte word carries 4 bytes of data and the tag of
+// the call, and an aligned 8-byte store arrives whole, so a receiver that sees the tag has the data -- no
+// fence, no separate flag, no second trip over the link.  A thread owns 8 elements (4 words).
 template <bool BF16>
 __global__ void __launch_bounds__(kCommThreads) qcomm_allreduce_kernel(const CommArgs c) {
     using T = typename Act16<BF16>::T;
@@ -44,54 +60,54 @@ __global__ void __launch_bounds__(kCommThreads) qcomm_allreduce_kernel(const Com
     const bool live = idx < c.elems;
     asm volatile("griddepcontrol.wait;" ::: "memory");      // the producer of `data` has finished
     const unsigned call = ld_relaxed_gpu(c.state);           // calls completed so far: the same on every rank
-    const unsigned half = call & 1u, tag = call + 1u;
-    const size_t half_elems = (size_t)c.world * c.max_elems;
-
-    // 1. my vector into my slot of every rank's receive buffer
-    uint4 mine = make_uint4(0u, 0u, 0u, 0u);
+    const unsigned half = call & 1u, tag = call + 1u;        // never 0: the buffers start zero-filled
+    const size_t rank_words = (size_t)c.max_elems / 2, half_words = (size_t)c.world * rank_words;
+    const size_t ll_off = plain_bytes(c.world, c.max_elems);
     if (live) {
-        mine = *reinterpret_cast<const uint4*>(static_cast<const T*>(c.data) + idx);
+        const unsigned long long hi = (unsigned long long)tag << 32;
+        const uint4 mine = *reinterpret_cast<const uint4*>(static_cast<const T*>(c.data) + idx);
         for (int p = 0; p < c.world; ++p) {
             const int peer = (c.rank + p) % c.world;          // start with my own buffer, spread the rest
-            T* dst = reinterpret_cast<T*>(c.slots[peer]) + half * half_elems + (size_t)c.rank * c.max_elems + idx;
-            *reinterpret_cast<uint4*>(dst) = mine;
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(c.slots[peer] + ll_off) + half * half_words +
+                                      (size_t)c.rank * rank_words + idx / 2;
+            st_relaxed_sys_v2(dst, hi | mine.x, hi | mine.y);
+            st_relaxed_sys_v2(dst + 2, hi | mine.z, hi | mine.w);
         }
-    }
-    __threadfence_system();                                  // my stores are visible system-wide before the flags
-    __syncthreads();
-    // 2. raise my flag for this CTA's chunk at every rank, then wait for everybody's flag here
-    if (tid < c.world) {
-        unsigned* f = c.flags[tid] + (half * c.world + c.rank) * QCOMM_MAX_BLOCKS + b;
-        st_release_sys(f, tag);
-    }
-    if (tid < c.world) {
-        const unsigned* f = c.flags[c.rank] + (half * c.world + tid) * QCOMM_MAX_BLOCKS + b;
-        int probes = 0;
-        while (ld_acquire_sys(f) != tag) {
-            if (++probes > c.wait_limit) { atomicExch(c.state + 2, 1u); break; }
-            __nanosleep(64);
-        }
-    }
-    __syncthreads();
-    // 3. add the slots in rank order: the same order, hence the same bits, on every rank
-    if (live) {
+        // collect: the slots of all ranks in rank order (the same order, hence the same bits, on every rank)
         float acc[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) acc[q] = 0.0f;
-        const T* base = reinterpret_cast<const T*>(c.slots[c.rank]) + half * half_elems + idx;
+        const unsigned long long* base = reinterpret_cast<const unsigned long long*>(c.slots[c.rank] + ll_off) + half * half_words + idx / 2;
+        bool gave_up = false;
         for (int r = 0; r < c.world; ++r) {
-            const uint4 v = ld_cg_u128(base + (size_t)r * c.max_elems);
-            const T* e = reinterpret_cast<const T*>(&v);
+            const unsigned long long* src = base + (size_t)r * rank_words;
+            unsigned long long w[4];
+            int probes = 0;
+            for (;;) {
+                ld_relaxed_sys_v2(src, w[0], w[1]);
+                ld_relaxed_sys_v2(src + 2, w[2], w[3]);
+                if ((unsigned)(w[0] >> 32) == tag && (unsigned)(w[1] >> 32) == tag && (unsigned)(w[2] >> 32) == tag &&
+                    (unsigned)(w[3] >> 32) == tag)
+                    break;
+                if (++probes > c.wait_limit) { gave_up = true; break; }
+                __nanosleep(32);
+            }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) acc[q] += Act16<BF16>::to_float(e[q]);
+            for (int q = 0; q < 4; ++q) {
+                const unsigned lo = (unsigned)w[q];
+                const T* e = reinterpret_cast<const T*>(&lo);
+                acc[2 * q] += Act16<BF16>::to_float(e[0]);
+                acc[2 * q + 1] += Act16<BF16>::to_float(e[1]);
+            }
         }
+        if (gave_up) atomicExch(c.state + 2, 1u);
         uint4 out;
         T* o = reinterpret_cast<T*>(&out);
 #pragma unroll
         for (int q = 0; q < 8; ++q) o[q] = Act16<BF16>::from_float(acc[q]);
         *reinterpret_cast<uint4*>(static_cast<T*>(c.data) + idx) = out;
     }
-    // 4. the last CTA of the launch advances the call counter (every CTA has read it by now)
+    // the last CTA of the launch advances the call counter (every CTA has read it by now)
     __syncthreads();
     if (tid == 0) {
         const unsigned old = atomicAdd(c.state + 1, 1u);
@@ -291,7 +307,10 @@ extern "C" int qcomm_allreduce_rmsnorm(const qcomm_group* g, const void* partial
     return check_launch("qcomm_allreduce_rmsnorm_kernel");
 }
 
-extern "C" size_t qcomm_slot_bytes(int world, int max_elems) { return (size_t)2 * world * max_elems * 2; }
+extern "C" size_t qcomm_slot_bytes(int world, int max_elems) {
+    // the plain area and, behind it, the area of self-validating words (8 bytes per 2 elements)
+    return plain_bytes(world, max_elems) + (size_t)2 * world * (max_elems / 2) * 8;
+}
 extern "C" size_t qcomm_flag_bytes(int world) { return (size_t)2 * world * QCOMM_MAX_BLOCKS * sizeof(unsigned); }
 extern "C" size_t qcomm_state_bytes(void) { return 256; }
 

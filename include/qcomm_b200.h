@@ -3,11 +3,14 @@
  * Tensor-parallel decode of the packed models splits o_proj / down_proj along K: every rank produces
  * a partial [M, hidden] result (16 - 64 KB) that must be summed over the ranks, 2 x layers times per
  * token.  At that size a collective is pure latency, so this one is a single kernel per rank:
- * every rank stores its vector into a slot of EVERY rank's receive buffer (plain 16-byte stores over
- * NVLink / NVSwitch), raises a flag there, waits -- a bounded time -- until the flags of all ranks
- * have arrived in its own buffer, and adds the slots in rank order (fp32 accumulation), so that all
- * ranks compute bit-identical sums.  Two buffer halves alternate from call to call; a rank cannot
- * run two calls ahead of another, so nothing is overwritten while it is still being read.
+ * every rank stores its vector into a slot of EVERY rank's receive buffer over NVLink / NVSwitch as
+ * self-validating 8-byte words -- 4 bytes of data and the 32-bit tag of the call; an aligned 8-byte
+ * store arrives whole, so whoever sees the tag has the data, and there is no fence, no separate
+ * flag and no second trip over the link -- then polls its own buffer, a bounded time, until the
+ * words of all ranks carry the call's tag, and adds them in rank order (fp32 accumulation), so that
+ * all ranks compute bit-identical sums.  Two buffer halves alternate from call to call; a rank
+ * cannot run two calls ahead of another, so nothing is overwritten while it is still being read.
+ * (qcomm_allreduce_rmsnorm keeps the plain-data-plus-flag protocol in its own part of the buffers.)
  *
  * Peer loads and stores only: no in-switch reduction or broadcast, no library kernel is handed a peer pointer.
  * The reference project has no multi-GPU path, so nothing here has a counterpart in it; the
@@ -38,7 +41,8 @@ typedef struct qcomm_group {
     int32_t rank, world;                 /* 1 <= world <= QCOMM_MAX_RANKS */
     int32_t max_elems;                   /* capacity of one slot in 16-bit elements, multiple of 8 */
     int32_t wait_limit;                  /* probes of a flag before giving up; 0 = default (about a second) */
-    void* slots[QCOMM_MAX_RANKS];        /* each qcomm_slot_bytes(world, max_elems): [2 halves][world][max_elems] x 16 bit */
+    void* slots[QCOMM_MAX_RANKS];        /* each qcomm_slot_bytes(world, max_elems): [2 halves][world][max_elems] x 16 bit of plain
+                                            data, then [2 halves][world][max_elems / 2] tagged 8-byte words */
     void* flags[QCOMM_MAX_RANKS];        /* each qcomm_flag_bytes(world): [2 halves][world][QCOMM_MAX_BLOCKS] uint32 */
     void* state;                         /* local, 256 bytes: call counter, finished-CTA counter, status word */
 } qcomm_group;
@@ -52,7 +56,7 @@ size_t qcomm_state_bytes(void);
  * or QGEMV_BF16.  Every rank of the group must issue the same sequence of calls.  Capturable in a
  * CUDA graph (the call counter lives in device memory).  The kernel waits for the preceding kernel
  * of the stream before it reads `data` and lets the following one start early (programmatic
- * dependent launch).  If a peer's flag does not arrive within the wait limit the kernel finishes
+ * dependent launch).  If a peer's words do not arrive within the wait limit the kernel finishes
  * anyway, with whatever the slot holds, and raises the status word. */
 int qcomm_allreduce(const qcomm_group* g, void* data, int64_t elems, int dtype, void* stream);
 
