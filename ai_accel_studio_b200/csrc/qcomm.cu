@@ -36,6 +36,79 @@ __device__ __forceinline__ unsigned ld_relaxed_gpu(const unsigned* p) {
     unsigned v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
 }
 
+// One-shot all-reduce, plain data + flags: every rank stores its vector into its slot of every rank's receive
+// buffer, makes the stores visible system-wide, raises a flag per rank (release), waits for the others' flags
+// (acquire, bounded) and adds the slots in rank order.  One polling thread per peer: the protocol of choice
+// from 4 ranks up (70B-shape decode on 8 GPUs: 131 tok/s against 118 with the tagged words below).
+template <bool BF16>
+__global__ void __launch_bounds__(kCommThreads) qcomm_allreduce_flags_kernel(const CommArgs c) {
+    using T = typename Act16<BF16>::T;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int tid = threadIdx.x, b = blockIdx.x;
+    const int idx = (b * kCommThreads + tid) * 8;            // first element of this thread
+    const bool live = idx < c.elems;
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // the producer of `data` has finished
+    const unsigned call = ld_relaxed_gpu(c.state);           // calls completed so far: the same on every rank
+    const unsigned half = call & 1u, tag = call + 1u;
+    const size_t half_elems = (size_t)c.world * c.max_elems;
+
+    // 1. my vector into my slot of every rank's receive buffer
+    uint4 mine = make_uint4(0u, 0u, 0u, 0u);
+    if (live) {
+        mine = *reinterpret_cast<const uint4*>(static_cast<const T*>(c.data) + idx);
+        for (int p = 0; p < c.world; ++p) {
+            const int peer = (c.rank + p) % c.world;          // start with my own buffer, spread the rest
+            T* dst = reinterpret_cast<T*>(c.slots[peer]) + half * half_elems + (size_t)c.rank * c.max_elems + idx;
+            *reinterpret_cast<uint4*>(dst) = mine;
+        }
+    }
+    __threadfence_system();                                  // my stores are visible system-wide before the flags
+    __syncthreads();
+    // 2. raise my flag for this CTA's chunk at every rank, then wait for everybody's flag here
+    if (tid < c.world) {
+        unsigned* f = c.flags[tid] + (half * c.world + c.rank) * QCOMM_MAX_BLOCKS + b;
+        st_release_sys(f, tag);
+    }
+    if (tid < c.world) {
+        const unsigned* f = c.flags[c.rank] + (half * c.world + tid) * QCOMM_MAX_BLOCKS + b;
+        int probes = 0;
+        while (ld_acquire_sys(f) != tag) {
+            if (++probes > c.wait_limit) { atomicExch(c.state + 2, 1u); break; }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    // 3. add the slots in rank order: the same order, hence the same bits, on every rank
+    if (live) {
+        float acc[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] = 0.0f;
+        const T* base = reinterpret_cast<const T*>(c.slots[c.rank]) + half * half_elems + idx;
+        for (int r = 0; r < c.world; ++r) {
+            const uint4 v = ld_cg_u128(base + (size_t)r * c.max_elems);
+            const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[q] += Act16<BF16>::to_float(e[q]);
+        }
+        uint4 out;
+        T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[q] = Act16<BF16>::from_float(acc[q]);
+        *reinterpret_cast<uint4*>(static_cast<T*>(c.data) + idx) = out;
+    }
+    // 4. the last CTA of the launch advances the call counter (every CTA has read it by now)
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned old = atomicAdd(c.state + 1, 1u);
+        if (old == gridDim.x - 1) {
+            c.state[1] = 0u;
+            __threadfence();
+            c.state[0] = tag;
+        }
+    }
+}
+
+
 // Bytes of the plain receive area (used by the fused all-reduce + RMS norm kernel with its flags) and of the
 // self-validating area behind it (used by qcomm_allreduce): [2 halves][world][max_elems / 2] words of 8 bytes,
 // each {two 16-bit elements, 32-bit call tag}.
@@ -346,8 +419,16 @@ extern "C" int qcomm_allreduce(const qcomm_group* g, void* data, int64_t elems, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = dtype == QGEMV_BF16 ? cudaLaunchKernelEx(&cfg, qcomm_allreduce_kernel<true>, c)
-                                              : cudaLaunchKernelEx(&cfg, qcomm_allreduce_kernel<false>, c);
+    // Two ranks: tagged words (one trip over the link; 98.4 against 92.9 tok/s on the 70B-shape decode).  More ranks:
+    // plain data + flags (every thread of the tagged version polls every peer, which costs more than the fence it saves).
+    const bool tagged = g->world <= 2;
+    cudaError_t e;
+    if (tagged)
+        e = dtype == QGEMV_BF16 ? cudaLaunchKernelEx(&cfg, qcomm_allreduce_kernel<true>, c)
+                                : cudaLaunchKernelEx(&cfg, qcomm_allreduce_kernel<false>, c);
+    else
+        e = dtype == QGEMV_BF16 ? cudaLaunchKernelEx(&cfg, qcomm_allreduce_flags_kernel<true>, c)
+                                : cudaLaunchKernelEx(&cfg, qcomm_allreduce_flags_kernel<false>, c);
     (void)e;
     return check_launch("qcomm_allreduce_kernel");
 }

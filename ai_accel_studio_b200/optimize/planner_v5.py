@@ -294,3 +294,32 @@ def collect_linear_inputs(model: nn.Module, input_ids_batches, device, max_rows=
     for h in hooks:
         h.remove()
     return {k: torch.cat(v, 0)[:max_rows] for k, v in captures.items() if v}
+
+
+def _demo():
+    """Decisions of the planner, timed gate included, for seeded random layers of decoder shapes on the current
+    CUDA device: one JSON line per layer (python -m ai_accel_studio_b200.optimize.planner_v5)."""
+    import argparse
+    import json
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", nargs="+", default=["4096x4096", "14336x4096", "4096x14336"], help="N x K of each layer")
+    ap.add_argument("--rows", type=int, default=64, help="calibration rows")
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("the timed gate needs a CUDA device")
+    for i, shape in enumerate(a.shapes):
+        n, k = (int(v) for v in shape.lower().split("x"))
+        g = torch.Generator().manual_seed(100 + i)
+        layer = nn.Linear(k, n, bias=False)
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(n, k, generator=g) * 0.02)
+        layer = layer.half().cuda()
+        x = torch.randn(a.rows, k, generator=g) * torch.exp(0.5 * torch.randn(k, generator=g))
+        d = decide_linear_v5(f"layer{i}_{n}x{k}", layer, x)
+        print(json.dumps(d.to_dict()), flush=True)
+        del layer
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    _demo()

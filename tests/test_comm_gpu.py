@@ -2,9 +2,9 @@
 
 On one GPU (this file's single-process tests) two ranks cannot run side by side -- kernels that wait
 for each other must never be separate launches on one device -- so the two-rank data path is
-checked in turns: the rank that goes first finds no partner and its bounded wait runs out (the
-status word says so and nothing hangs), the rank that goes second finds the first one's vector and
-flag in place and must produce the exact sum.  The real thing (two processes, two GPUs, compared
+checked in turns: a rank that goes early finds partners missing and its bounded wait runs out (the
+status word says so and nothing hangs), the rank that goes last finds everybody's vector in place
+and must produce the exact sum.  The real thing (two processes, two GPUs, compared
 with NCCL) is the last test and needs two devices.
 """
 import os
@@ -100,26 +100,35 @@ def test_fused_allreduce_rmsnorm_single_rank_equals_the_plain_kernels():
     comm.close()
 
 
-def test_two_ranks_in_turns_and_the_wait_that_runs_out():
-    world, n = 2, 8192
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_in_turns_and_the_wait_that_runs_out(world):
+    """All ranks of a group on one device, one after the other (2 ranks: tagged words; 4 ranks: data + flags).
+    Whoever goes before the last finds partners missing: its bounded wait runs out, the status word says so,
+    nothing hangs.  The rank that goes last finds everybody's vector in place and must produce the exact sum."""
+    n = 8192
     bufs = [_buffers(world, n) for _ in range(world)]
     peers = [(b[0].data_ptr(), b[1].data_ptr()) for b in bufs]
-    # a short wait limit: the rank that goes first gives up after ~100 probes instead of a second
+    # a short wait limit: a rank without partners gives up after ~100 probes instead of a second
     ranks = [OneShotAllReduce(rank=r, world=world, max_elems=n, peers=peers, wait_limit=100) for r in range(world)]
     g = torch.Generator(device="cuda").manual_seed(3)
-    for rnd in range(4):                            # alternates the buffer halves; who goes first alternates too
+    for rnd in range(4):                            # alternates the buffer halves; the order of the ranks rotates
         xs = [torch.randn(n, generator=g, device="cuda").half() for _ in range(world)]
-        want = (xs[0].float() + xs[1].float()).half()
-        first, second = (0, 1) if rnd % 2 == 0 else (1, 0)
+        acc = torch.zeros(n, device="cuda")
+        for x in xs:                                # rank order, fp32: what the kernel computes
+            acc = acc + x.float()
+        want = acc.half()
+        order = [(rnd + i) % world for i in range(world)]
         ys = [x.clone() for x in xs]
-        ranks[first](ys[first])
-        torch.cuda.synchronize()                    # the launch ended by itself although its partner never came
-        assert ranks[first].status() == 1           # ... and reported the wait that ran out
-        assert ranks[first].status() == 0           # reading clears the word
-        ranks[second](ys[second])
+        for r in order[:-1]:
+            ranks[r](ys[r])
+            torch.cuda.synchronize()                # the launch ended by itself although partners never came
+            assert ranks[r].status() == 1           # ... and reported the wait that ran out
+            assert ranks[r].status() == 0           # reading clears the word
+        last = order[-1]
+        ranks[last](ys[last])
         torch.cuda.synchronize()
-        assert ranks[second].status() == 0          # the partner's vector and flag were already there
-        assert torch.equal(ys[second], want), rnd
+        assert ranks[last].status() == 0            # every partner's vector was already there
+        assert torch.equal(ys[last], want), rnd
     # the device is as usable as before
     assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
     for r in ranks:
