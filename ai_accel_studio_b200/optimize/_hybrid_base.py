@@ -143,11 +143,20 @@ class HybridPackedLinear(nn.Module):
                 del self.__dict__[name]     # plain None placeholders make way for buffers
             if name in self._buffers:
                 del self._buffers[name]
+        self.__dict__.pop("_call", None)
         self.register_buffer("res_u", res_u.detach().to(dev, torch.float16).contiguous())
         self.register_buffer("res_v", res_v.detach().to(dev, torch.float16).contiguous())
         self.residual_rank = int(res_u.shape[1])
 
+    _LAUNCH_OPERANDS = frozenset(("packed", "scales", "bias", "outlier_idx", "outlier_weight", "res_u", "res_v", "residual_rank"))
+
+    def __setattr__(self, name, value):
+        if name in HybridPackedLinear._LAUNCH_OPERANDS:
+            self.__dict__.pop("_call", None)          # the prepared launch holds the old tensor's address
+        super().__setattr__(name, value)
+
     def _apply(self, fn, *args, **kwargs):
+        self.__dict__.pop("_call", None)
         out = super()._apply(fn, *args, **kwargs)
         if self.packed.is_cuda:
             from .. import ops
@@ -157,22 +166,21 @@ class HybridPackedLinear(nn.Module):
     def _fused(self, xp: torch.Tensor) -> torch.Tensor:
         from .. import _cabi, ops
         if not torch.compiler.is_compiling():
-            # eager: the prepared launch of this module for activations of this shape (rebuilt whenever a
-            # buffer has moved or a setting has changed)
+            # eager: the prepared launch of this module for activations of this shape.  It is dropped whenever a
+            # buffer is replaced (__setattr__, _apply, set_residual) and rebuilt when a setting has changed.
+            d = self.__dict__
             pre = self.prefetch_next
-            key = (xp.shape[0], xp.dtype, xp.stride(0), xp.device, self.packed.data_ptr(), self.scales.data_ptr(),
-                   self.outlier_weight.data_ptr(), self.residual_rank, 0 if self.res_u is None else self.res_u.data_ptr(),
-                   0 if self.bias is None else self.bias.data_ptr(), self.kernel, getattr(self, "debug", 0), self.gated_pairs,
-                   0 if pre is None else pre.data_ptr())
-            call = self.__dict__.get("_call")
-            if call is None or call.key != key:
+            sig = (xp.shape[0], xp.dtype, xp.stride(0), xp.device, self.kernel, d.get("debug", 0), self.gated_pairs, id(pre))
+            call = d.get("_call")
+            if call is None or call.key != sig or call.keep[0] is not d["_buffers"]["packed"]:
                 has_o = self.outlier_idx.numel() > 0
                 call = ops.prepare_call(xp, self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
                                         self.outlier_weight if has_o else None,
                                         self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
                                         self.bits, self.group_size, self.original_k, 3 if self.gated_pairs else 0,
-                                        self._kernel_code(), pre, key)
-                self.__dict__["_call"] = call
+                                        self._kernel_code(), pre, sig)
+                call.keep = (self.packed, self.scales, self.bias, self.outlier_idx, self.outlier_weight, self.res_u, self.res_v, pre)
+                d["_call"] = call
             return call.run(xp)
         return ops.gemv(xp, self.packed, self.scales, self.bias, self.outlier_idx if self.outlier_idx.numel() else None,
                         self.outlier_weight if self.outlier_idx.numel() else None,

@@ -131,6 +131,7 @@ def merge_gate_up(gate, up):
         t = getattr(fused, name, None)
         if t is not None and t.shape[0] == 2 * n:
             fused._buffers[name] = t[perm].contiguous()
+    fused.__dict__.pop("_call", None)               # buffers were replaced behind the module's back
     fused.gated_pairs = True
     fused.out_features = n
     return fused

@@ -118,3 +118,29 @@ def test_vocabulary_sharded_greedy_token_two_ranks():
         ret = mgr.dict()
         mp.spawn(_vocab_shard_rank, args=(2, port, ret), nprocs=2, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def test_native_decode_step_recognises_what_it_can_run(monkeypatch):
+    """Host-side gatekeeping of the decode-step kernels: Llama / Qwen2 style decoders qualify, anything the
+    kernels do not cover is named, and a CPU decoder keeps the framework's forward."""
+    from ai_accel_studio_b200 import decode_step as ds
+    from ai_accel_studio_b200.runtime_v5 import StaticGraphDecoder
+    monkeypatch.setitem(mt.SHAPES, "tiny", dict(family="llama", layers=2, hidden=128, inter=256, heads=2, kv_heads=1,
+                                                head_dim=64, vocab=96, qkv_bias=False))
+    model = mt.build_fp16_model("tiny", "cpu")
+    assert ds.unsupported_reason(model) is None
+    dec = StaticGraphDecoder(model.float(), 1, 16, device="cpu")
+    dec.prefill(torch.randint(0, 96, (1, 4)))
+    assert dec.native is None and dec.native_reason == "not a CUDA device"
+    with pytest.raises(NotImplementedError):
+        forced = StaticGraphDecoder(model, 1, 16, device="cpu", native_step=True)
+        forced.prefill(torch.randint(0, 96, (1, 4)))
+    model.model.layers[0].self_attn.q_norm = torch.nn.Identity()
+    assert "q / k normalisation" in ds.unsupported_reason(model)
+    del model.model.layers[0].self_attn.q_norm
+    model.model.layers[1].mlp.act_fn = torch.nn.GELU()
+    assert "SwiGLU" in ds.unsupported_reason(model)
+    monkeypatch.setitem(mt.SHAPES, "odd-heads", dict(family="llama", layers=1, hidden=96, inter=128, heads=2, kv_heads=1,
+                                                     head_dim=48, vocab=64, qkv_bias=False))
+    assert "head_dim 48" in ds.unsupported_reason(mt.build_fp16_model("odd-heads", "cpu"))
+    assert "not a decoder" in ds.unsupported_reason(torch.nn.Linear(4, 4))

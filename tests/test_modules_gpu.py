@@ -262,3 +262,31 @@ def test_gated_pair_epilogue(bits, dtype):
                  fused.res_v, bits, 128, k, ops.ACT_SILU_MUL, _cabi.KERNEL["simt"])
     assert e.value.code == -2
     assert ops.workspace_status("cuda") == 0
+
+
+def test_prepared_launch_follows_the_module():
+    """The eager decode path keeps a prepared launch per module; replacing a buffer, attaching a residual,
+    changing the kernel or the activation shape must all be seen by the next call."""
+    torch.manual_seed(31)
+    k, n = 1024, 512
+    a = HybridInt4Linear(nn.Linear(k, n, bias=True), 128, None, 8).cuda()
+    b = HybridInt4Linear(nn.Linear(k, n, bias=True), 128, None, 8).cuda()
+    x = torch.randn(1, k).half().cuda()
+    ya, yb = a(x), b(x)
+    assert not torch.equal(ya, yb) and torch.equal(a(x), ya)               # second call: the prepared launch
+    a.packed = b.packed.clone()                                             # every operand swapped for b's, one at a time
+    a.scales = b.scales.clone()
+    a.bias = b.bias.clone()
+    a.outlier_idx = b.outlier_idx.clone()
+    a.outlier_weight = b.outlier_weight.clone()
+    assert torch.equal(a(x), yb)
+    a.set_residual(torch.randn(n, 4) * 0.05, torch.randn(4, k) * 0.05)
+    y_res = a(x)
+    assert not torch.equal(y_res, yb)
+    x4 = torch.randn(4, k).half().cuda()
+    assert a(x4).shape == (4, n)
+    assert torch.equal(a(x), y_res)                                          # back to one row
+    a.kernel = "simt"
+    assert (a(x).float() - y_res.float()).abs().max() < 2e-3                 # another kernel, same answer to rounding
+    moved = a.cpu().cuda()
+    assert (moved(x).float() - y_res.float()).abs().max() < 2e-3
