@@ -43,8 +43,9 @@ def select_outliers(module: nn.Module, w: torch.Tensor, activation_rms, outlier_
 
 
 class HybridPackedLinear(nn.Module):
-    """Common forward: M <= 4 -> one fused GEMV launch; larger M -> CUDA dequantisation into the
-    activation dtype + library GEMMs for the base, outlier and residual terms."""
+    """Common forward: M <= 4 -> one fused GEMV launch; up to ``chunked_max_rows`` rows -> one fused launch per
+    four rows; larger M -> CUDA dequantisation into the activation dtype + library GEMMs for the base, outlier
+    and residual terms."""
 
     bits: int = 0
     residual_rank: int = 0
@@ -55,6 +56,8 @@ class HybridPackedLinear(nn.Module):
     # Optional hint for the decode path: a static tensor (normally the packed codes of the module that
     # runs next) announced to L2 while this module's GEMV runs; see model_tools.chain_weight_prefetch.
     prefetch_next = None
+    # Largest row count served by repeated fused GEMVs (groups of four rows) instead of the dequantise + GEMM route.
+    chunked_max_rows: int = 16
     # Set by siblings.merge_gate_up: the rows are (8 gate, 8 up) blocks of a feed-forward block's two
     # input projections and forward returns silu(gate(x)) * up(x), of width out_features = rows / 2.
     gated_pairs: bool = False
@@ -241,6 +244,27 @@ class HybridPackedLinear(nn.Module):
             if xp.stride(1) != 1:
                 xp = xp.contiguous()
             y = self._fused(xp)
+        elif xflat.shape[0] <= self.chunked_max_rows:
+            y = self._fused_chunks(xflat)
         else:
             y = self._dense(xflat)
         return y.reshape(*shape[:-1], self.out_features)
+
+    def _fused_chunks(self, xflat: torch.Tensor) -> torch.Tensor:
+        """5 .. ``chunked_max_rows`` rows (a decode batch beyond the kernel's four): the fused GEMV over groups of
+        four rows, written into one result.  The packed weights of one Linear stay in L2 between the launches,
+        where dequantising the whole matrix for every token (the M > 4 route of the reference,
+        ``ai_accel_lab/optimize/hybrid_int4.py:36-37``) would write and re-read 2 bytes per weight."""
+        from .. import ops
+        xp = xflat if self.padded_k == self.original_k else F.pad(xflat, (0, self.padded_k - self.original_k))
+        if xp.stride(1) != 1:
+            xp = xp.contiguous()
+        has_o = self.outlier_idx.numel() > 0
+        act = 3 if self.gated_pairs else 0
+        y = torch.empty((xp.shape[0], self.out_features), dtype=xp.dtype, device=xp.device)
+        for lo in range(0, xp.shape[0], 4):
+            ops.gemv_into(xp[lo:lo + 4], self.packed, self.scales, self.bias, self.outlier_idx if has_o else None,
+                          self.outlier_weight if has_o else None,
+                          self.res_u if self.residual_rank else None, self.res_v if self.residual_rank else None,
+                          self.bits, self.group_size, self.original_k, act, self._kernel_code(), y[lo:lo + 4], self.prefetch_next)
+        return y

@@ -34,13 +34,17 @@ def test_modules_reproduce_reference_outputs(small_cases):
         kw = dict(bias=z[nm + ".bias"] if c["bias"] else None, outlier_idx=z[nm + ".outlier_idx"],
                   outlier_weight=z[nm + ".outlier_weight"],
                   res_u=z[nm + ".res_u"] if c["rank"] else None, res_v=z[nm + ".res_v"] if c["rank"] else None)
-        for m in (1, 2, 3, 4, 6):       # 6 rows takes the dequantise + GEMM path
+        for m in (1, 2, 3, 4, 6):       # 6 rows: two fused launches (four rows + two rows)
             x = torch.from_numpy(z[f"{nm}.x{m}"])
             y = mod(x.cuda())
             assert y.dtype == torch.float16 and tuple(y.shape) == (m, c["n"])
             ref = O.gemv_f32(x.numpy(), host, **kw)
-            if m <= 4:
-                assert_within_tolerance(y.float().cpu().numpy(), ref, f"{nm} m={m}")
+            assert_within_tolerance(y.float().cpu().numpy(), ref, f"{nm} m={m}")
+            if m == 6:                  # the dequantise + GEMM route (what more than 16 rows take), forced
+                mod.chunked_max_rows = 4
+                yd = mod(x.cuda())
+                del mod.chunked_max_rows
+                assert np.abs(yd.float().cpu().numpy() - z[f"{nm}.y{m}"].astype(np.float32)).max() < 8e-3, (nm, m)
             # against what the reference module returned on the CPU (fp16 arithmetic on both sides)
             assert np.abs(y.float().cpu().numpy() - z[f"{nm}.y{m}"].astype(np.float32)).max() < 8e-3, (nm, m)
         x3 = torch.from_numpy(z[nm + ".x3d"])
@@ -253,10 +257,11 @@ def test_gated_pair_epilogue(bits, dtype):
         assert float((err / (tol * want.abs() + 1e-2)).max()) <= 1.0, float(err.max())
         sep = torch.nn.functional.silu(gate(x)) * up(x)
         assert float((y.float() - sep.float()).abs().max()) <= 2e-2 * float(sep.float().abs().max()) + 1e-3
-    x8 = torch.randn(9, k).to(dtype).cuda()                                        # M > 4: dequantise + GEMM, then the same pairing
-    y8, sep8 = fused(x8), torch.nn.functional.silu(gate(x8)) * up(x8)
-    assert y8.shape == (9, n)
-    assert float((y8.float() - sep8.float()).abs().max()) <= 2e-2 * float(sep8.float().abs().max()) + 1e-3
+    for rows in (9, 20):                    # 9 rows: three fused launches; 20 rows: dequantise + GEMM, then the same pairing
+        x8 = torch.randn(rows, k).to(dtype).cuda()
+        y8, sep8 = fused(x8), torch.nn.functional.silu(gate(x8)) * up(x8)
+        assert y8.shape == (rows, n)
+        assert float((y8.float() - sep8.float()).abs().max()) <= 2e-2 * float(sep8.float().abs().max()) + 1e-3
     with pytest.raises(_cabi.QgemvError) as e:                                      # no gated epilogue in the CUDA-core kernel
         ops.gemv(x8[:1].contiguous(), fused.packed, fused.scales, fused.bias, fused.outlier_idx, fused.outlier_weight, fused.res_u,
                  fused.res_v, bits, 128, k, ops.ACT_SILU_MUL, _cabi.KERNEL["simt"])
