@@ -181,6 +181,14 @@ def decide_linear_v4(name, layer, sample_x, group_sizes=(128, 64, 32), outliers=
                            "kept dense: local guard failed")
 
 
+def build_plan_v4(model, captures, group_sizes=(128, 64, 32), outliers=(0, 8, 16, 32), residual_ranks=(0, 4, 8),
+                  nmse_limit=.06, cosine_limit=.96, min_compression=1.5):
+    """One ``LayerDecisionV4`` per captured ``nn.Linear`` (``ai_accel_lab/optimize/planner_v4.py:73-81``)."""
+    mods = dict(model.named_modules())
+    return [decide_linear_v4(name, mods[name], x, group_sizes, outliers, residual_ranks, nmse_limit, cosine_limit, min_compression)
+            for name, x in captures.items() if isinstance(mods.get(name), nn.Linear)]
+
+
 def _cuda_ms(fn, repeats):
     for _ in range(3):
         fn()

@@ -69,3 +69,20 @@ def test_build_plan_and_capture():
     plan = pl.build_plan_v5(model, caps)
     assert [d.name for d in plan] == ["0", "2"]                         # the ReLU is not a Linear
     assert all(isinstance(d, pl.LayerDecisionV5) for d in plan)
+
+
+def test_capture_then_plan_on_a_decoder(monkeypatch):
+    """collect_linear_inputs on a tiny decoder (token ids instead of texts), then both planners over the captures."""
+    from ai_accel_studio_b200 import model_tools as mt
+    monkeypatch.setitem(mt.SHAPES, "tiny", dict(family="llama", layers=1, hidden=128, inter=256, heads=2, kv_heads=1,
+                                                head_dim=64, vocab=96, qkv_bias=False))
+    model = mt.build_fp16_model("tiny", "cpu").float()
+    ids = [torch.randint(0, 96, (2, 12), generator=torch.Generator().manual_seed(i)) for i in range(6)]
+    caps = pl.collect_linear_inputs(model, ids, "cpu", max_rows=40, target_tokens=("q_proj", "down_proj"))
+    assert set(caps) == {"model.layers.0.self_attn.q_proj", "model.layers.0.mlp.down_proj"}
+    assert caps["model.layers.0.self_attn.q_proj"].shape == (40, 128)        # four forward calls of 24 rows, cut to 40
+    assert caps["model.layers.0.mlp.down_proj"].shape == (40, 256) and caps["model.layers.0.mlp.down_proj"].dtype == torch.float32
+    p5 = pl.build_plan_v5(model, caps, group_sizes=(64,), outliers=(0, 8))
+    p4 = pl.build_plan_v4(model, caps, group_sizes=(64,), outliers=(0, 8))
+    assert [d.name for d in p5] == [d.name for d in p4] == list(caps)
+    assert all(d.decode_speedup is None or d.method == "fp16" for d in p5)    # CPU: the gate reports "not measured"
