@@ -317,3 +317,14 @@ def test_direct_c_abi_call_and_plan_name():
     assert not ws[1024:1024 + 4 * 16384].any()            # scratch invariant: arrival counters back to zero
     p.kernel = _cabi.KERNEL["simt"]
     assert _cabi.plan_name(p).startswith("simt_int4")
+
+
+def test_reference_selftest_probes_pass():
+    """The hot-path probes of the reference's self test (its inputs, its comparison, its thresholds)."""
+    from ai_accel_studio_b200.selftest import run_selftest
+    torch.manual_seed(0)
+    report = run_selftest()
+    assert report["ok"], report
+    by = {p["name"]: p for p in report["probes"]}
+    assert by["decode-int2-v4"]["max_abs_error"] < 0.5 and by["decode-int4-v5"]["max_abs_error"] < 0.35
+    assert by["decode-int2-v4"]["cosine"] > 0.999 and by["decode-int4-v5"]["cosine"] > 0.999 and by["cuda-graph"]["ok"]

@@ -182,3 +182,11 @@ def test_c_abi_rejects_bad_problems_without_launching():
     assert l.qgemv_run(ctypes.byref(p), None) == -4  # no workspace
     assert l.qdequant(2, None, 0, None, 0, 1, 4, 4, 4, None, 4, 0, None) == -1
     assert l.qunpack_codes(5, 256, 1, 1, 4, 256, 4, None) == -1
+
+
+def test_selftest_reports_a_missing_device_instead_of_falling_back():
+    from ai_accel_studio_b200.selftest import run_selftest
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    report = run_selftest()
+    assert report["ok"] is False and report["probes"][0]["name"] == "cuda" and "no CPU implementation" in report["probes"][0]["error"]
