@@ -189,17 +189,51 @@ def build_plan_v4(model, captures, group_sizes=(128, 64, 32), outliers=(0, 8, 16
             for name, x in captures.items() if isinstance(mods.get(name), nn.Linear)]
 
 
-def _cuda_ms(fn, repeats):
-    for _ in range(3):
-        fn()
+GATE_WARMUPS, GATE_DECODE_REPEATS, GATE_PREFILL_REPEATS, GATE_PREFILL_ROWS = 3, 24, 12, 32   # the reference's protocol
+
+
+def _mean_ms(call, repeats: int, warmups: int = GATE_WARMUPS) -> float:
+    """Mean milliseconds of ``call`` over ``repeats`` eager invocations between two CUDA events."""
+    for _ in range(warmups):
+        call()
     torch.cuda.synchronize()
-    st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    st.record()
+    begin, end = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+    begin.record()
     for _ in range(repeats):
-        fn()
-    en.record()
-    en.synchronize()
-    return float(st.elapsed_time(en)) / repeats
+        call()
+    end.record()
+    end.synchronize()
+    return begin.elapsed_time(end) / repeats
+
+
+@dataclass
+class GateTiming:
+    """Eager milliseconds of the dense layer and of the packed candidate for one decode row and for a small prefill."""
+    dense_decode: float
+    packed_decode: float
+    dense_prefill: float
+    packed_prefill: float
+
+    def speedups(self, expected_decode_tokens: int):
+        """(decode, prefill, projected over one prefill + ``expected_decode_tokens`` decode steps)."""
+        tiny = 1e-9
+        dense_total = self.dense_prefill + expected_decode_tokens * self.dense_decode
+        packed_total = self.packed_prefill + expected_decode_tokens * self.packed_decode
+        return (self.dense_decode / max(self.packed_decode, tiny), self.dense_prefill / max(self.packed_prefill, tiny),
+                dense_total / max(packed_total, tiny))
+
+
+def time_gate(layer, candidate, x) -> GateTiming:
+    """Time ``candidate`` against ``F.linear`` with the dense layer's weight on the first row and on the first
+    ``GATE_PREFILL_ROWS`` rows of ``x`` (``ai_accel_lab/optimize/planner_v5.py:36-52``)."""
+    weight = layer.weight.to(x.dtype)
+    bias = None if layer.bias is None else layer.bias.to(x.dtype)
+    timings = {}
+    for label, rows, repeats in (("decode", 1, GATE_DECODE_REPEATS), ("prefill", min(GATE_PREFILL_ROWS, x.shape[0]), GATE_PREFILL_REPEATS)):
+        sample = x[:rows].contiguous()
+        timings["dense_" + label] = _mean_ms(lambda: F.linear(sample, weight, bias), repeats)
+        timings["packed_" + label] = _mean_ms(lambda: candidate(sample), repeats)
+    return GateTiming(**timings)
 
 
 def runtime_speedups(layer, candidate, x, expected_decode_tokens=64):
@@ -207,17 +241,7 @@ def runtime_speedups(layer, candidate, x, expected_decode_tokens=64):
     when the layer is not on a CUDA device (the reference's convention)."""
     if layer.weight.device.type != "cuda":
         return None, None, None
-    bias = None if layer.bias is None else layer.bias.to(x.dtype)
-    x1 = x[:1].contiguous()
-    xp = x[:min(32, x.shape[0])].contiguous()
-    w = layer.weight.to(x.dtype)
-    d1 = _cuda_ms(lambda: F.linear(x1, w, bias), 24)
-    q1 = _cuda_ms(lambda: candidate(x1), 24)
-    dp = _cuda_ms(lambda: F.linear(xp, w, bias), 12)
-    qp = _cuda_ms(lambda: candidate(xp), 12)
-    decode, prefill = d1 / max(q1, 1e-9), dp / max(qp, 1e-9)
-    projected = (dp + d1 * expected_decode_tokens) / max(qp + q1 * expected_decode_tokens, 1e-9)
-    return decode, prefill, projected
+    return time_gate(layer, candidate, x).speedups(expected_decode_tokens)
 
 
 def gate_passes(decode, projected, min_decode_speedup=1.0, min_projected_speedup=1.02) -> bool:

@@ -86,3 +86,13 @@ def test_capture_then_plan_on_a_decoder(monkeypatch):
     p4 = pl.build_plan_v4(model, caps, group_sizes=(64,), outliers=(0, 8))
     assert [d.name for d in p5] == [d.name for d in p4] == list(caps)
     assert all(d.decode_speedup is None or d.method == "fp16" for d in p5)    # CPU: the gate reports "not measured"
+
+
+def test_gate_arithmetic():
+    t = pl.GateTiming(dense_decode=0.016, packed_decode=0.013, dense_prefill=0.016, packed_prefill=0.045)
+    decode, prefill, projected = t.speedups(64)
+    assert decode == pytest.approx(16 / 13) and prefill == pytest.approx(16 / 45)
+    assert projected == pytest.approx((0.016 + 64 * 0.016) / (0.045 + 64 * 0.013))
+    assert pl.gate_passes(decode, projected) and not pl.gate_passes(*pl.GateTiming(1.0, 1.1, 1.0, 1.0).speedups(64)[::2])
+    layer = torch.nn.Linear(8, 8)
+    assert pl.runtime_speedups(layer, layer, torch.randn(4, 8)) == (None, None, None)      # CPU: not measured
