@@ -49,7 +49,7 @@ class HybridPackedLinear(nn.Module):
 
     bits: int = 0
     residual_rank: int = 0
-    # Measurement aid: when set, the decode path (M <= 4) launches nothing and returns a zero buffer
+    # Measurement aid: when set, the decode path (every row count served by fused GEMVs) launches nothing and returns a zero buffer
     # of the right shape, so that replaying a decode step with and without the packed GEMVs tells how
     # much of the step they are.  Never set in production.
     skip_gemv: bool = False
@@ -233,7 +233,7 @@ class HybridPackedLinear(nn.Module):
             raise RuntimeError("fp16/bf16 activations required")
         shape = x.shape
         xflat = x.reshape(-1, shape[-1])
-        if xflat.shape[0] <= 4 and HybridPackedLinear.skip_gemv:
+        if xflat.shape[0] <= self.chunked_max_rows and HybridPackedLinear.skip_gemv:
             key = (xflat.shape[0], x.dtype)
             cache = self.__dict__.setdefault("_skip_out", {})
             if key not in cache:

@@ -146,3 +146,33 @@ def test_decoder_rewiring_builds_gated_feed_forward():
     assert isinstance(model[0].mlp, GatedFeedForward) and model[0].mlp.gate_up.gated_pairs
     assert not isinstance(model[1].mlp, GatedFeedForward)        # another activation: only the launches are merged
     assert fuse_decoder_siblings(nn.ModuleList([Layer(nn.SiLU())]), gated=False) == 1
+
+
+def test_merge_algebra_holds_for_random_sibling_sets():
+    """Property test: for random sibling sets (sizes, outlier sets, residual ranks, biases) the merged module's
+    reconstructed weight is the row-wise concatenation of the siblings', and its bias their concatenation."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=25, deadline=None)
+    @given(bits=st.sampled_from([2, 4]), sizes=st.lists(st.integers(1, 40), min_size=2, max_size=4),
+           ocs=st.lists(st.integers(0, 9), min_size=4, max_size=4), ranks=st.lists(st.sampled_from([0, 2, 5]), min_size=4, max_size=4),
+           seed=st.integers(0, 10 ** 6))
+    def check(bits, sizes, ocs, ranks, seed):
+        torch.manual_seed(seed)
+        k = 128
+        cls = HybridInt2Linear if bits == 2 else HybridInt4Linear
+        mods = []
+        for i, n in enumerate(sizes):
+            m = cls(nn.Linear(k, n, bias=bool((seed + i) % 2)), 64, None, ocs[i])
+            if ranks[i]:
+                m.set_residual(torch.randn(n, ranks[i]) * 0.05, torch.randn(ranks[i], k) * 0.05)
+            mods.append(m)
+        fused, out_sizes = merge_packed(mods)
+        assert out_sizes == sizes and fused.out_features == sum(sizes)
+        want = torch.cat([m.effective_weight() for m in mods], 0)
+        assert torch.allclose(fused.effective_weight(), want, atol=1e-6)
+        if fused.bias is not None:
+            want_b = torch.cat([m.bias if m.bias is not None else torch.zeros(m.out_features, dtype=torch.float16) for m in mods])
+            assert torch.equal(fused.bias, want_b)
+        assert fused.outlier_idx.numel() % 8 == 0                   # rows stay 16-byte aligned for the prefetching kernel
+    check()
