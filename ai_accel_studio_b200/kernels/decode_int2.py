@@ -59,8 +59,9 @@ def _fused(bits, x, pw, bias, outlier_idx, outlier_weight, res_u, res_v, activat
     if torch.compiler.is_compiling():          # the registered operator only where a tracer needs it
         return ops.gemv(x, pw.packed, pw.scales, b16, oi, ow, ru, rv, bits, pw.group_size, pw.original_k, act,
                         _cabi.KERNEL[kernel])
-    # Eager: reuse the prepared launch for these operands.  Keyed by addresses AND shapes, so a
-    # recycled address with other dimensions never meets a stale struct.
+    # Eager: reuse the prepared launch for these operands.  Keyed by the addresses AND shapes of the tensors of THIS
+    # call, so a hit means the struct's pointers are exactly the ones passed now (the cache holds no tensor alive, and
+    # a recycled address with other dimensions never meets a stale struct).
     ptr = lambda t: 0 if t is None else t.data_ptr()
     key = (bits, x.shape[0], x.dtype, x.stride(0), dev, pw.packed.data_ptr(), tuple(pw.packed.shape), pw.packed.stride(0),
            pw.scales.data_ptr(), tuple(pw.scales.shape), pw.group_size, pw.original_k, ptr(b16), ptr(oi), ptr(ow),
@@ -71,7 +72,6 @@ def _fused(bits, x, pw, bias, outlier_idx, outlier_weight, res_u, res_v, activat
             _CALLS.clear()
         call = _CALLS[key] = ops.prepare_call(x, pw.packed, pw.scales, b16, oi, ow, ru, rv, bits, pw.group_size,
                                               pw.original_k, act, _cabi.KERNEL[kernel], None, key)
-        call.keep = (pw.packed, pw.scales, b16, oi, ow, ru, rv)      # the struct's pointers stay valid while it is cached
     return call.run(x)
 
 
