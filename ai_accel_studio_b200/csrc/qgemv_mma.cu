@@ -147,6 +147,9 @@ __device__ __forceinline__ void stage_activations(const MmaArgs& p, unsigned cha
 #pragma unroll
         for (int r = 0; r < RC; ++r) {
             const bool live = vm[r] >= 0;
+            // a warp whose lanes all lie past the last item (the second item slot of a thread when the items
+            // just fill the CTA once) skips the slot: warp-uniform, so the shuffles below stay converged
+            if (!__any_sync(0xffffffffu, live)) continue;
             const int mrow = live ? vm[r] : 0, grp = vg[r], tq = vt[r];
             float f[EPI];
             float part = 0.0f, big = 0.0f;
